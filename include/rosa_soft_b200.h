@@ -1,0 +1,130 @@
+/*
+ * rosa_soft_b200 -- C ABI of the sm_100a implementation of the rosa_soft operator
+ * family (hard ROSA suffix routing forward, dense surrogate VJP backward, the packed
+ * variable-length variant and batched hard inference).
+ *
+ * Conventions
+ *   - All data pointers are DEVICE pointers on the current CUDA device unless a
+ *     parameter says otherwise.  `stream` is a cudaStream_t passed as void*.
+ *   - The library allocates nothing: every entry point that needs scratch takes a
+ *     caller-owned `workspace` of at least `*_workspace_bytes(...)` bytes
+ *     (256-byte aligned).  Workspace contents are undefined between calls.
+ *   - Every entry point only enqueues work on `stream`; none synchronises.
+ *   - Return value 0 = success; non-zero = argument error, nothing was enqueued and
+ *     rosa_b200_last_error() describes the problem (thread-local string).
+ *   - Sequences: either `cu_seqlens == NULL` (dense: `num_seq` sequences of
+ *     `uniform_len` tokens, N = num_seq * uniform_len, packed symbols laid out
+ *     [num_seq, H, uniform_len]) or a device int32 array of num_seq + 1 offsets
+ *     (packed: symbols laid out [H, N]).  Offsets are validated on the device; an
+ *     inconsistent array makes every kernel a no-op for the call (outputs zero) and
+ *     sets the status word that rosa_b200_read_status() returns.  Nothing traps.
+ *   - Layouts: query/key [N, H, D], value [N, Hv, Dv], output / grad_output
+ *     [N, H, Dv], all contiguous, element type given by `dtype`.
+ */
+#ifndef ROSA_SOFT_B200_H_
+#define ROSA_SOFT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ROSA_B200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define ROSA_B200_API __attribute__((visibility("default")))
+#else
+#define ROSA_B200_API
+#endif
+
+enum rosa_b200_dtype { ROSA_B200_F32 = 0, ROSA_B200_F16 = 1, ROSA_B200_BF16 = 2 };
+
+/* status word values reported by rosa_b200_read_status */
+enum rosa_b200_status {
+  ROSA_B200_STATUS_OK = 0,
+  ROSA_B200_STATUS_BAD_FIRST_OFFSET = 1, /* cu_seqlens[0] != 0            */
+  ROSA_B200_STATUS_NOT_MONOTONE = 2,     /* cu_seqlens decreases somewhere */
+  ROSA_B200_STATUS_BAD_LAST_OFFSET = 3   /* cu_seqlens[-1] != N            */
+};
+
+ROSA_B200_API int rosa_b200_abi_version(void);
+ROSA_B200_API const char* rosa_b200_last_error(void);
+
+/* ---------------------------------------------------------------- hard forward
+ * Replaces hard_forward_cuda / hard_forward_varlen_cuda
+ * (reference rosa_soft/csrc/rosa_soft.cpp:11-24, kernels
+ * rosa_soft/csrc/cuda/rosa_soft_kernels.cu:202-241, 311-531, 1766-1920).
+ * Writes the hard output (sign of the routed value row, or exact zero), the two
+ * packed symbol tensors that are part of the operator's return contract, and --
+ * optionally -- the global token index of the routed value row per (token, head)
+ * (-1 = null route; local route index = route_token - sequence start). */
+ROSA_B200_API size_t rosa_b200_hard_forward_workspace_bytes(int64_t N, int H, int64_t num_seq);
+
+ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, const void* value, int dtype,
+                           int64_t N, int H, int D, int Hv, int Dv, const int32_t* cu_seqlens,
+                           int64_t num_seq, int64_t uniform_len, int64_t max_suffix_length,
+                           void* output, int32_t* packed_query, int32_t* packed_key,
+                           int32_t* route_token /* nullable, [N, H] */, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------- surrogate VJP
+ * Replaces surrogate_vjp_cuda / surrogate_vjp_varlen_cuda
+ * (reference rosa_soft/csrc/rosa_soft.cpp:26-55, kernels
+ * rosa_soft/csrc/cuda/rosa_soft_kernels.cu:534-1731, planners :1923-2638).
+ * gradient_mask: bit0 query, bit1 key, bit2 value; outputs whose bit is clear may
+ * be NULL.  Gradients are float32 in the layout of the corresponding input and
+ * include the softsign Jacobian 1/(1+|x|)^2.  `dropout_seed` is a device int64
+ * scalar, required iff dropout_p > 0.  `dropout_batch_offset` / `dropout_head_offset`
+ * are added to the sequence ordinal / head index inside the dropout counter so a
+ * shard of a larger problem reproduces the masks of the unsharded run.
+ * Reduction order is fixed: results are bitwise reproducible run to run. */
+ROSA_B200_API size_t rosa_b200_surrogate_vjp_workspace_bytes(int64_t N, int H, int D, int Hv, int Dv,
+                                               int64_t num_seq, int64_t uniform_len,
+                                               int64_t max_suffix_length, int gradient_mask);
+
+ROSA_B200_API int rosa_b200_surrogate_vjp(const void* query, const void* key, const void* value,
+                            const void* grad_output, int dtype, int64_t N, int H, int D, int Hv,
+                            int Dv, const int32_t* cu_seqlens, int64_t num_seq,
+                            int64_t uniform_len, int64_t max_suffix_length,
+                            const int32_t* packed_query, const int32_t* packed_key,
+                            const int64_t* dropout_seed, float scale, float dropout_p,
+                            float mismatch_scale, int gradient_mask,
+                            int64_t dropout_batch_offset, int64_t dropout_head_offset,
+                            float* grad_query, float* grad_key, float* grad_value, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
+/* --------------------------------------------------------- hard inference batch
+ * GPU equivalent of feeding whole streams to RosaRuntime.update_packed
+ * (reference rosa_soft/csrc/rosa_runtime.cpp:333-482; match semantics :41-45,
+ * :103-133; successor payload :455-467).  Symbols are token-major [N, H] words of up
+ * to 32 bits; payload [N, Hp, Dp] float32.  Writes the payload row following the
+ * match (zeros for null) to out [N, H, Dp] (nullable) and the matched key end
+ * position local to its stream (-1 = null) to matched_end [N, H]. */
+ROSA_B200_API size_t rosa_b200_hard_inference_workspace_bytes(int64_t N, int H, int64_t num_seq);
+
+ROSA_B200_API int rosa_b200_hard_inference(const uint32_t* query_symbols, const uint32_t* key_symbols,
+                             const float* payload, int64_t N, int H, int Hp, int Dp,
+                             const int32_t* cu_seqlens, int64_t num_seq, int64_t uniform_len,
+                             int64_t max_suffix_length, float* out, int64_t* matched_end,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* Per-kernel timing for benchmarks (no counterpart in the reference, which times whole
+ * steps with CUDA events in benchmarks/rosa_soft.py:151-173).  While enabled, every kernel
+ * launch made by this library is bracketed by a CUDA event pair on the launching stream.
+ * rosa_b200_profile_collect waits for the recorded events, returns the number of distinct
+ * kernel names and fills, per name, the summed device time in milliseconds and the launch
+ * count; it then forgets the records.  Off by default; do not enable around stream capture. */
+ROSA_B200_API void rosa_b200_profile_enable(int on);
+ROSA_B200_API int rosa_b200_profile_collect(const char** names, float* total_ms, int* launches,
+                                            int capacity);
+
+/* Copies the status word of the last call that used `workspace` to the host.
+ * This is the one entry point that synchronises `stream`. */
+ROSA_B200_API int rosa_b200_read_status(const void* workspace, void* stream, int* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ROSA_SOFT_B200_H_ */

@@ -1,0 +1,196 @@
+"""ctypes front-end of ``librosa_soft_b200.so`` (the C ABI of include/rosa_soft_b200.h).
+
+This is the binding a non-torch host would write; the test-suite and the benchmark use it to
+drive the library with raw device pointers (taken from torch tensors, which only serve as
+device memory here).  Loading fails loudly when the shared object is absent.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "librosa_soft_b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+
+EXPORTED_SYMBOLS = (
+    "rosa_b200_abi_version",
+    "rosa_b200_last_error",
+    "rosa_b200_hard_forward_workspace_bytes",
+    "rosa_b200_hard_forward",
+    "rosa_b200_surrogate_vjp_workspace_bytes",
+    "rosa_b200_surrogate_vjp",
+    "rosa_b200_hard_inference_workspace_bytes",
+    "rosa_b200_hard_inference",
+    "rosa_b200_read_status",
+    "rosa_b200_profile_enable",
+    "rosa_b200_profile_collect",
+)
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise OSError(f"{LIB_PATH} not found: run `python rosa_soft_b200/build.py`")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i64, i32, f32, sz = (ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float,
+                             ctypes.c_size_t)
+    lib.rosa_b200_abi_version.restype = i32
+    lib.rosa_b200_last_error.restype = ctypes.c_char_p
+    lib.rosa_b200_hard_forward_workspace_bytes.restype = sz
+    lib.rosa_b200_hard_forward_workspace_bytes.argtypes = [i64, i32, i64]
+    lib.rosa_b200_hard_forward.restype = i32
+    lib.rosa_b200_hard_forward.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, i32, vp, i64, i64,
+                                           i64, vp, vp, vp, vp, vp, sz, vp]
+    lib.rosa_b200_surrogate_vjp_workspace_bytes.restype = sz
+    lib.rosa_b200_surrogate_vjp_workspace_bytes.argtypes = [i64, i32, i32, i32, i32, i64, i64, i64,
+                                                            i32]
+    lib.rosa_b200_surrogate_vjp.restype = i32
+    lib.rosa_b200_surrogate_vjp.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i32, i32, vp, i64,
+                                            i64, i64, vp, vp, vp, f32, f32, f32, i32, i64, i64, vp,
+                                            vp, vp, vp, sz, vp]
+    lib.rosa_b200_hard_inference_workspace_bytes.restype = sz
+    lib.rosa_b200_hard_inference_workspace_bytes.argtypes = [i64, i32, i64]
+    lib.rosa_b200_hard_inference.restype = i32
+    lib.rosa_b200_hard_inference.argtypes = [vp, vp, vp, i64, i32, i32, i32, vp, i64, i64, i64, vp,
+                                             vp, vp, sz, vp]
+    lib.rosa_b200_read_status.restype = i32
+    lib.rosa_b200_read_status.argtypes = [vp, vp, ctypes.POINTER(i32)]
+    lib.rosa_b200_profile_enable.restype = None
+    lib.rosa_b200_profile_enable.argtypes = [i32]
+    lib.rosa_b200_profile_collect.restype = i32
+    lib.rosa_b200_profile_collect.argtypes = [ctypes.POINTER(ctypes.c_char_p),
+                                              ctypes.POINTER(f32), ctypes.POINTER(i32), i32]
+    _lib = lib
+    return lib
+
+
+def profile_enable(on: bool) -> None:
+    load().rosa_b200_profile_enable(1 if on else 0)
+
+
+def profile_collect() -> dict:
+    """{kernel name: (total milliseconds, launches)} of the launches recorded since the last call."""
+    cap = 64
+    names = (ctypes.c_char_p * cap)()
+    ms = (ctypes.c_float * cap)()
+    launches = (ctypes.c_int * cap)()
+    n = load().rosa_b200_profile_collect(names, ms, launches, cap)
+    return {names[i].decode(): (float(ms[i]), int(launches[i])) for i in range(n)}
+
+
+def last_error() -> str:
+    return load().rosa_b200_last_error().decode()
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(f"rosa_soft_b200 C ABI error {rc}: {last_error()}")
+
+
+def dtype_code(torch_dtype) -> int:
+    import torch
+
+    return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[torch_dtype]
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def hard_forward(q, k, v, cu_seqlens, max_suffix_length, want_routes=True, stream=None):
+    """Device tensors in the packed view: q,k [N,H,D], v [N,Hv,Dv]; dense batches pass
+    ``cu_seqlens=(B, T)``.  Returns (out, packed_q, packed_k, route_token)."""
+    import torch
+
+    lib = load()
+    N, H, D = q.shape
+    Hv, Dv = v.shape[1:]
+    if isinstance(cu_seqlens, tuple):
+        S, T = cu_seqlens
+        cu, sym_shape = None, (S, H, T)
+    else:
+        S, T = cu_seqlens.numel() - 1, 0
+        cu, sym_shape = cu_seqlens, (H, N)
+    out = torch.empty((N, H, Dv), dtype=q.dtype, device=q.device)
+    pq = torch.empty(sym_shape, dtype=torch.int32, device=q.device)
+    pk = torch.empty_like(pq)
+    routes = torch.empty((N, H), dtype=torch.int32, device=q.device) if want_routes else None
+    nbytes = lib.rosa_b200_hard_forward_workspace_bytes(N, H, S)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    st = stream if stream is not None else torch.cuda.current_stream(q.device).cuda_stream
+    check(lib.rosa_b200_hard_forward(_ptr(q), _ptr(k), _ptr(v), dtype_code(q.dtype), N, H, D, Hv,
+                                     Dv, _ptr(cu), S, T, int(max_suffix_length), _ptr(out),
+                                     _ptr(pq), _ptr(pk), _ptr(routes), _ptr(ws), nbytes,
+                                     ctypes.c_void_p(st)))
+    return out, pq, pk, routes, ws
+
+
+def surrogate_vjp(q, k, v, go, cu_seqlens, packed_q, packed_k, max_suffix_length, scale=1.0,
+                  dropout_p=0.0, mismatch_scale=3.0, seed=None, mask=7, batch_offset=0,
+                  head_offset=0, stream=None):
+    """Returns float32 (dq, dk, dv); entries masked off are ``None``."""
+    import torch
+
+    lib = load()
+    N, H, D = q.shape
+    Hv, Dv = v.shape[1:]
+    if isinstance(cu_seqlens, tuple):
+        S, T = cu_seqlens
+        cu = None
+    else:
+        S, T = cu_seqlens.numel() - 1, 0
+        cu = cu_seqlens
+    f32 = dict(dtype=torch.float32, device=q.device)
+    dq = torch.empty((N, H, D), **f32) if mask & 1 else None
+    dk = torch.empty((N, H, D), **f32) if mask & 2 else None
+    dv = torch.empty((N, Hv, Dv), **f32) if mask & 4 else None
+    nbytes = lib.rosa_b200_surrogate_vjp_workspace_bytes(N, H, D, Hv, Dv, S, T,
+                                                         int(max_suffix_length), mask)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    st = stream if stream is not None else torch.cuda.current_stream(q.device).cuda_stream
+    check(lib.rosa_b200_surrogate_vjp(_ptr(q), _ptr(k), _ptr(v), _ptr(go), dtype_code(q.dtype), N,
+                                      H, D, Hv, Dv, _ptr(cu), S, T, int(max_suffix_length),
+                                      _ptr(packed_q), _ptr(packed_k), _ptr(seed), float(scale),
+                                      float(dropout_p), float(mismatch_scale), mask,
+                                      int(batch_offset), int(head_offset), _ptr(dq), _ptr(dk),
+                                      _ptr(dv), _ptr(ws), nbytes, ctypes.c_void_p(st)))
+    return dq, dk, dv, ws
+
+
+def hard_inference(qsym, ksym, payload, cu_seqlens, max_suffix_length, stream=None):
+    """qsym, ksym int32 [N,H]; payload float32 [N,Hp,Dp]. Returns (out, matched_end)."""
+    import torch
+
+    lib = load()
+    N, H = qsym.shape
+    Hp, Dp = payload.shape[1:]
+    if isinstance(cu_seqlens, tuple):
+        S, T = cu_seqlens
+        cu = None
+    else:
+        S, T = cu_seqlens.numel() - 1, 0
+        cu = cu_seqlens
+    out = torch.empty((N, H, Dp), dtype=torch.float32, device=qsym.device)
+    end = torch.empty((N, H), dtype=torch.int64, device=qsym.device)
+    nbytes = lib.rosa_b200_hard_inference_workspace_bytes(N, H, S)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=qsym.device)
+    st = stream if stream is not None else torch.cuda.current_stream(qsym.device).cuda_stream
+    check(lib.rosa_b200_hard_inference(_ptr(qsym), _ptr(ksym), _ptr(payload), N, H, Hp, Dp,
+                                       _ptr(cu), S, T, int(max_suffix_length), _ptr(out), _ptr(end),
+                                       _ptr(ws), nbytes, ctypes.c_void_p(st)))
+    return out, end, ws
+
+
+def read_status(ws, stream=None) -> int:
+    import torch
+
+    st = stream if stream is not None else torch.cuda.current_stream(ws.device).cuda_stream
+    status = ctypes.c_int(0)
+    check(load().rosa_b200_read_status(_ptr(ws), ctypes.c_void_p(st), ctypes.byref(status)))
+    return status.value

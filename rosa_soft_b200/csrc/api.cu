@@ -1,0 +1,335 @@
+// C ABI of librosa_soft_b200.so: argument checks, workspace carve-up and kernel
+// sequencing.  No allocation, no synchronisation (except rosa_b200_read_status).
+#include <algorithm>
+#include <cmath>
+#include <limits>
+
+#include "common.cuh"
+
+namespace rosa {
+const char* get_error();
+void profile_enable(bool on);
+int profile_collect(const char** names, float* total_ms, int* launches, int capacity);
+}
+
+using namespace rosa;
+
+namespace {
+
+constexpr size_t kPartialBudgetBytes = (size_t)6 << 30;  // target size of the VJP partial buffers
+
+struct FwdLayout {
+  PlanLayout plan;
+  size_t best_off, qt_off, kt_off;
+  size_t bytes;
+  int items_upper;
+};
+
+int64_t fwd_items_upper(int64_t N, int64_t S, int64_t uniform_len, bool dense) {
+  if (dense) return S * (uniform_len >= 2 ? (uniform_len - 1 + kFwdBand - 1) / kFwdBand : 0);
+  return N / kFwdBand + S;
+}
+
+FwdLayout fwd_layout(int64_t N, int H, int64_t S, bool transposed_symbols) {
+  FwdLayout l;
+  l.plan = plan_layout(0, S);
+  size_t off = l.plan.bytes;
+  l.best_off = off;
+  off = align_up(off + (size_t)N * H * sizeof(unsigned long long));
+  l.qt_off = l.kt_off = 0;
+  if (transposed_symbols) {
+    l.qt_off = off;
+    off = align_up(off + (size_t)N * H * sizeof(int32_t));
+    l.kt_off = off;
+    off = align_up(off + (size_t)N * H * sizeof(int32_t));
+  }
+  l.bytes = off;
+  return l;
+}
+
+struct VjpLayout {
+  PlanLayout plan;
+  size_t vbits_off, ckpt_off, stat_off, rowstat_off, ring_off, dq_off, dk_off, dv_off;
+  size_t ring_bytes;
+  size_t bytes;
+  int bands_per_item;
+  int vwords;
+  int ring_slots;
+  int64_t items_upper;  // per head
+};
+
+// Upper bounds that depend on shapes only (the packed path never reads cu_seqlens on
+// the host): items, partial-row slots and checkpoint blocks per head.
+void vjp_bounds(int64_t N, int64_t S, int64_t uniform_len, bool dense, int64_t item_diag,
+                int64_t* items, int64_t* rows, int64_t* cks) {
+  if (dense) {
+    const int64_t per = uniform_len >= 2 ? (uniform_len - 1 + item_diag - 1) / item_diag : 0;
+    *items = S * per;
+    *rows = S * per * uniform_len;
+    *cks = S * vjp_ck_count(uniform_len);
+  } else {
+    // sum_s ceil((L_s-1)/id) <= N/id + S ; sum_s items_s L_s <= N^2/id + N
+    *items = N / item_diag + S;
+    *rows = (N / item_diag + 1) * N;
+    // the per-sequence count is super-additive up to rounding: sum_s ck(L_s) <= ck(N) + slack
+    *cks = vjp_ck_count(N) + 2 * (N / kVjpRows) + 4 * S + 8;
+  }
+}
+
+VjpLayout vjp_layout(int64_t N, int H, int D, int Hv, int Dv, int64_t S, int64_t uniform_len,
+                     bool dense, int64_t W, int mask) {
+  VjpLayout l;
+  l.plan = plan_layout(0, S);
+  l.vwords = (Dv + 31) / 32;
+  const int64_t max_len = dense ? uniform_len : N;
+  l.ring_slots = (W <= max_len - 2) ? (int)(W + 1) : 0;
+  const size_t per_row = sizeof(float4) + sizeof(float) * ((mask & 1 ? D : 0) + (mask & 2 ? D : 0) +
+                                                            (mask & 4 ? Dv : 0));
+  int g = 1;
+  int64_t items = 0, rows = 0, cks = 0;
+  for (;; g *= 2) {
+    vjp_bounds(N, S, uniform_len, dense, (int64_t)g * kVjpBand, &items, &rows, &cks);
+    if ((size_t)rows * H * per_row <= kPartialBudgetBytes || (int64_t)g * kVjpBand >= max_len) break;
+  }
+  l.bands_per_item = g;
+  l.items_upper = items;
+  size_t off = l.plan.bytes;
+  l.vbits_off = off;
+  off = align_up(off + (size_t)N * Hv * l.vwords * sizeof(uint32_t));
+  l.ckpt_off = off;
+  off = align_up(off + (size_t)cks * H * kVjpBand * sizeof(int2));
+  l.stat_off = off;
+  off = align_up(off + (size_t)rows * H * sizeof(float4));
+  l.rowstat_off = off;
+  off = align_up(off + (size_t)N * H * sizeof(float4));
+  l.ring_off = off;
+  l.ring_bytes = (size_t)items * H * l.ring_slots * kVjpBand * sizeof(float);
+  off = align_up(off + l.ring_bytes);
+  l.dq_off = off;
+  if (mask & 1) off = align_up(off + (size_t)rows * H * D * sizeof(float));
+  l.dk_off = off;
+  if (mask & 2) off = align_up(off + (size_t)rows * H * D * sizeof(float));
+  l.dv_off = off;
+  if (mask & 4) off = align_up(off + (size_t)rows * H * Dv * sizeof(float));
+  l.bytes = off;
+  return l;
+}
+
+int check_problem(int64_t N, int H, int D, int Hv, int Dv, const int32_t* cu, int64_t S,
+                  int64_t uniform_len, int64_t W, int dtype) {
+  ROSA_REQUIRE(dtype >= ROSA_B200_F32 && dtype <= ROSA_B200_BF16,
+               "dtype must be float32, float16 or bfloat16");
+  ROSA_REQUIRE(N > 0 && H > 0 && Hv > 0 && Dv > 0, "N, H, Hv and Dv must be positive");
+  ROSA_REQUIRE(D >= 1 && D <= 32, "query/key bit dimension must be in [1, 32]");
+  ROSA_REQUIRE(H % Hv == 0, "query heads must be divisible by value heads");
+  ROSA_REQUIRE(H <= 65535, "head count exceeds the CUDA grid limit");
+  ROSA_REQUIRE(S >= 1, "at least one sequence is required");
+  ROSA_REQUIRE(N * H <= std::numeric_limits<int32_t>::max(), "N * H must fit in int32");
+  ROSA_REQUIRE(W >= 1, "max_suffix_length must be >= 1");
+  if (cu == nullptr)
+    ROSA_REQUIRE(uniform_len >= 1 && S * uniform_len == N,
+                 "dense description needs num_seq * uniform_len == N");
+  return 0;
+}
+
+inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+
+}  // namespace
+
+extern "C" {
+
+ROSA_B200_API int rosa_b200_abi_version(void) { return ROSA_B200_ABI_VERSION; }
+
+ROSA_B200_API const char* rosa_b200_last_error(void) { return rosa::get_error(); }
+
+ROSA_B200_API size_t rosa_b200_hard_forward_workspace_bytes(int64_t N, int H, int64_t num_seq) {
+  return fwd_layout(N, H, num_seq, false).bytes;
+}
+
+ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, const void* value, int dtype,
+                           int64_t N, int H, int D, int Hv, int Dv, const int32_t* cu_seqlens,
+                           int64_t num_seq, int64_t uniform_len, int64_t max_suffix_length,
+                           void* output, int32_t* packed_query, int32_t* packed_key,
+                           int32_t* route_token, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  if (int rc = check_problem(N, H, D, Hv, Dv, cu_seqlens, num_seq, uniform_len, max_suffix_length,
+                             dtype))
+    return rc;
+  ROSA_REQUIRE(query && key && value && output && packed_query && packed_key && workspace,
+               "null pointer argument");
+  const bool dense = cu_seqlens == nullptr;
+  const FwdLayout l = fwd_layout(N, H, num_seq, false);
+  ROSA_REQUIRE(workspace_bytes >= l.bytes, "workspace too small: need %zu bytes, got %zu", l.bytes,
+               workspace_bytes);
+  cudaStream_t st = as_stream(stream);
+  char* ws = static_cast<char*>(workspace);
+
+  FwdArgs a{};
+  a.plan = make_plan(workspace, l.plan, cu_seqlens, N, num_seq, uniform_len, kFwdBand);
+  a.q = query; a.k = key; a.v = value; a.dtype = dtype;
+  a.N = N; a.H = H; a.D = D; a.Hv = Hv; a.Dv = Dv;
+  a.W = (int)std::min<int64_t>(max_suffix_length, dense ? uniform_len : N);
+  a.out = output; a.packed_q = packed_query; a.packed_k = packed_key;
+  a.route_token = route_token;
+  a.best = reinterpret_cast<unsigned long long*>(ws + l.best_off);
+  a.sym_seq_stride = dense ? (int64_t)H * uniform_len : 0;
+  a.sym_head_stride = dense ? uniform_len : N;
+
+  launch_build_plan(a.plan, st);
+  ROSA_CUDA_OK(cudaGetLastError());
+  ROSA_CUDA_OK(cudaMemsetAsync(a.best, 0, (size_t)N * H * sizeof(unsigned long long), st));
+  if (int rc = launch_pack_symbols(query, key, dtype, N, H, D, dense, uniform_len, packed_query,
+                                   packed_key, st))
+    return rc;
+  if (int rc = launch_hard_match(a, (int)fwd_items_upper(N, num_seq, uniform_len, dense), st))
+    return rc;
+  return launch_gather_output(a, st);
+}
+
+ROSA_B200_API size_t rosa_b200_hard_inference_workspace_bytes(int64_t N, int H, int64_t num_seq) {
+  return fwd_layout(N, H, num_seq, true).bytes;
+}
+
+ROSA_B200_API int rosa_b200_hard_inference(const uint32_t* query_symbols, const uint32_t* key_symbols,
+                             const float* payload, int64_t N, int H, int Hp, int Dp,
+                             const int32_t* cu_seqlens, int64_t num_seq, int64_t uniform_len,
+                             int64_t max_suffix_length, float* out, int64_t* matched_end,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  if (int rc = check_problem(N, H, 32, Hp, Dp, cu_seqlens, num_seq, uniform_len,
+                             max_suffix_length, ROSA_B200_F32))
+    return rc;
+  ROSA_REQUIRE(query_symbols && key_symbols && matched_end && workspace, "null pointer argument");
+  ROSA_REQUIRE(out == nullptr || payload != nullptr, "payload is required when out is given");
+  const bool dense = cu_seqlens == nullptr;
+  const FwdLayout l = fwd_layout(N, H, num_seq, true);
+  ROSA_REQUIRE(workspace_bytes >= l.bytes, "workspace too small: need %zu bytes, got %zu", l.bytes,
+               workspace_bytes);
+  cudaStream_t st = as_stream(stream);
+  char* ws = static_cast<char*>(workspace);
+
+  FwdArgs a{};
+  // symbols are transposed to [H, N] whatever the sequence description: the matcher
+  // only needs a per-sequence base and a head stride
+  a.plan = make_plan(workspace, l.plan, cu_seqlens, N, num_seq, uniform_len, kFwdBand);
+  a.N = N; a.H = H; a.D = 32; a.Hv = Hp; a.Dv = Dp;
+  a.W = (int)std::min<int64_t>(max_suffix_length, dense ? uniform_len : N);
+  a.packed_q = reinterpret_cast<int32_t*>(ws + l.qt_off);
+  a.packed_k = reinterpret_cast<int32_t*>(ws + l.kt_off);
+  a.best = reinterpret_cast<unsigned long long*>(ws + l.best_off);
+  a.sym_seq_stride = dense ? uniform_len : 0;  // [H, N] with sequence s starting at s * T
+  a.sym_head_stride = N;
+
+  launch_build_plan(a.plan, st);
+  ROSA_CUDA_OK(cudaGetLastError());
+  ROSA_CUDA_OK(cudaMemsetAsync(a.best, 0, (size_t)N * H * sizeof(unsigned long long), st));
+  if (int rc = launch_transpose_symbols(query_symbols, key_symbols, N, H, a.packed_q, a.packed_k,
+                                        st))
+    return rc;
+  if (int rc = launch_hard_match(a, (int)fwd_items_upper(N, num_seq, uniform_len, dense), st))
+    return rc;
+  return launch_inference_finish(a.plan, a.best, payload, N, H, Hp, Dp, out, matched_end, st);
+}
+
+ROSA_B200_API size_t rosa_b200_surrogate_vjp_workspace_bytes(int64_t N, int H, int D, int Hv, int Dv,
+                                               int64_t num_seq, int64_t uniform_len,
+                                               int64_t max_suffix_length, int gradient_mask) {
+  const bool dense = uniform_len > 0;
+  const int64_t W = std::min<int64_t>(max_suffix_length, dense ? uniform_len : N);
+  return vjp_layout(N, H, D, Hv, Dv, num_seq, uniform_len, dense, W, gradient_mask).bytes;
+}
+
+ROSA_B200_API int rosa_b200_surrogate_vjp(const void* query, const void* key, const void* value,
+                            const void* grad_output, int dtype, int64_t N, int H, int D, int Hv,
+                            int Dv, const int32_t* cu_seqlens, int64_t num_seq,
+                            int64_t uniform_len, int64_t max_suffix_length,
+                            const int32_t* packed_query, const int32_t* packed_key,
+                            const int64_t* dropout_seed, float scale, float dropout_p,
+                            float mismatch_scale, int gradient_mask,
+                            int64_t dropout_batch_offset, int64_t dropout_head_offset,
+                            float* grad_query, float* grad_key, float* grad_value, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  if (int rc = check_problem(N, H, D, Hv, Dv, cu_seqlens, num_seq, uniform_len, max_suffix_length,
+                             dtype))
+    return rc;
+  ROSA_REQUIRE(gradient_mask >= 1 && gradient_mask <= 7,
+               "gradient_mask must be an integer bit mask in [1, 7]");
+  ROSA_REQUIRE(query && key && value && grad_output && packed_query && packed_key && workspace,
+               "null pointer argument");
+  ROSA_REQUIRE(!(gradient_mask & 1) || grad_query, "grad_query is required by gradient_mask");
+  ROSA_REQUIRE(!(gradient_mask & 2) || grad_key, "grad_key is required by gradient_mask");
+  ROSA_REQUIRE(!(gradient_mask & 4) || grad_value, "grad_value is required by gradient_mask");
+  ROSA_REQUIRE(scale > 0.0f && std::isfinite(scale), "scale must be finite and > 0");
+  ROSA_REQUIRE(mismatch_scale > 0.0f && std::isfinite(mismatch_scale),
+               "mismatch_scale must be finite and > 0");
+  ROSA_REQUIRE(dropout_p >= 0.0f && dropout_p < 1.0f, "dropout_p must be in [0, 1)");
+  ROSA_REQUIRE((dropout_p > 0.0f) == (dropout_seed != nullptr),
+               "dropout_seed must be given exactly when dropout_p > 0");
+  const bool dense = cu_seqlens == nullptr;
+  if (!dense) uniform_len = 0;
+  const int64_t W = std::min<int64_t>(max_suffix_length, dense ? uniform_len : N);
+  const VjpLayout l = vjp_layout(N, H, D, Hv, Dv, num_seq, uniform_len, dense, W, gradient_mask);
+  ROSA_REQUIRE(workspace_bytes >= l.bytes, "workspace too small: need %zu bytes, got %zu", l.bytes,
+               workspace_bytes);
+  ROSA_REQUIRE(l.items_upper <= std::numeric_limits<int32_t>::max(), "too many work items");
+  cudaStream_t st = as_stream(stream);
+  char* ws = static_cast<char*>(workspace);
+
+  VjpArgs a{};
+  a.plan = make_plan(workspace, l.plan, cu_seqlens, N, num_seq, uniform_len,
+                     l.bands_per_item * kVjpBand);
+  a.q = query; a.k = key; a.v = value; a.go = grad_output; a.dtype = dtype;
+  a.N = N; a.H = H; a.D = D; a.Hv = Hv; a.Dv = Dv;
+  a.W = (int)W;
+  a.group = H / Hv;
+  a.bands_per_item = l.bands_per_item;
+  a.qsym = packed_query; a.ksym = packed_key;
+  a.sym_seq_stride = dense ? (int64_t)H * uniform_len : 0;
+  a.sym_head_stride = dense ? uniform_len : N;
+  a.vbits = reinterpret_cast<uint32_t*>(ws + l.vbits_off);
+  a.vwords = l.vwords;
+  a.seed = dropout_seed;
+  a.scale = scale;
+  a.dropout_p = dropout_p;
+  a.inv_keep = 1.0f / (1.0f - dropout_p);
+  a.mismatch_scale = mismatch_scale;
+  a.mask = gradient_mask;
+  a.batch_offset = (uint32_t)dropout_batch_offset;
+  a.head_offset = (uint32_t)dropout_head_offset;
+  a.ckpt = reinterpret_cast<int2*>(ws + l.ckpt_off);
+  a.stat_part = reinterpret_cast<float4*>(ws + l.stat_off);
+  a.rowstat = reinterpret_cast<float4*>(ws + l.rowstat_off);
+  a.ring = reinterpret_cast<float*>(ws + l.ring_off);
+  a.ring_slots = l.ring_slots;
+  a.dq_part = reinterpret_cast<float*>(ws + l.dq_off);
+  a.dk_part = reinterpret_cast<float*>(ws + l.dk_off);
+  a.dv_part = reinterpret_cast<float*>(ws + l.dv_off);
+  a.dq = grad_query; a.dk = grad_key; a.dv = grad_value;
+
+  launch_build_plan(a.plan, st);
+  ROSA_CUDA_OK(cudaGetLastError());
+  if (l.ring_bytes) ROSA_CUDA_OK(cudaMemsetAsync(a.ring, 0, l.ring_bytes, st));
+  if (int rc = launch_pack_value_bits(value, dtype, N, Hv, Dv, a.vbits, a.vwords, st)) return rc;
+  if (int rc = launch_vjp_sweep1(a, (int)l.items_upper, st)) return rc;
+  if (int rc = launch_vjp_rowstats(a, st)) return rc;
+  if (int rc = launch_vjp_sweep2(a, (int)l.items_upper, st)) return rc;
+  return launch_vjp_finalize(a, st);
+}
+
+ROSA_B200_API void rosa_b200_profile_enable(int on) { rosa::profile_enable(on != 0); }
+
+ROSA_B200_API int rosa_b200_profile_collect(const char** names, float* total_ms, int* launches,
+                                            int capacity) {
+  return rosa::profile_collect(names, total_ms, launches, capacity);
+}
+
+ROSA_B200_API int rosa_b200_read_status(const void* workspace, void* stream, int* status) {
+  ROSA_REQUIRE(workspace && status, "null pointer argument");
+  int32_t host = 0;
+  ROSA_CUDA_OK(cudaMemcpyAsync(&host, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost,
+                               as_stream(stream)));
+  ROSA_CUDA_OK(cudaStreamSynchronize(as_stream(stream)));
+  *status = host;
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,278 @@
+// Hard forward of the rosa_soft operator: sign-binarise Q/K into packed symbols, find the
+// latest among the longest causal suffix matches within the horizon, gather the sign of
+// the routed value row.  Replaces pack_sign_bits_pair_kernel, exact_suffix_length,
+// merge_hard_route and hard_forward_kernel of the reference
+// (rosa_soft/csrc/cuda/rosa_soft_kernels.cu:202-241, 311-531).
+//
+// Matching uses the exact diagonal run-length recurrence
+//     len(i, a) = (q_i == k_{a-1}) ? min(len(i-1, a-1) + 1, W) : 0
+// instead of re-walking every suffix: one thread owns several diagonals, a warp sits
+// on one query row at a time, the per-row winner is reduced with redux.sync and merged
+// across bands with one 64-bit integer atomicMax (order independent, hence exact and
+// deterministic).
+#include "common.cuh"
+
+namespace rosa {
+
+namespace {
+
+// ------------------------------------------------------------------ packing
+template <typename T>
+__device__ __forceinline__ bool positive(T x);
+template <>
+__device__ __forceinline__ bool positive<float>(float x) { return x > 0.0f; }
+template <>
+__device__ __forceinline__ bool positive<__half>(__half x) { return __half2float(x) > 0.0f; }
+template <>
+__device__ __forceinline__ bool positive<__nv_bfloat16>(__nv_bfloat16 x) {
+  return __bfloat162float(x) > 0.0f;
+}
+
+// One thread per (token, head); threads of a warp read consecutive D-vectors.
+template <typename T>
+__global__ void pack_symbols_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t N,
+                                    int H, int D, int dense, int64_t uniform_len,
+                                    int32_t* __restrict__ pq, int32_t* __restrict__ pk) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= N * H) return;
+  const int64_t token = idx / H;
+  const int h = (int)(idx - token * H);
+  const T* qr = q + idx * D;
+  const T* kr = k + idx * D;
+  uint32_t wq = 0, wk = 0;
+  for (int d = 0; d < D; ++d) {
+    wq |= (uint32_t)positive<T>(qr[d]) << d;
+    wk |= (uint32_t)positive<T>(kr[d]) << d;
+  }
+  int64_t dst;
+  if (dense) {
+    const int64_t b = token / uniform_len, t = token - b * uniform_len;
+    dst = (b * H + h) * uniform_len + t;
+  } else {
+    dst = (int64_t)h * N + token;
+  }
+  pq[dst] = (int32_t)wq;
+  pk[dst] = (int32_t)wk;
+}
+
+// token-major [N, H] symbols -> head-major [H, N]
+__global__ void transpose_symbols_kernel(const uint32_t* __restrict__ q,
+                                         const uint32_t* __restrict__ k, int64_t N, int H,
+                                         int32_t* __restrict__ qt, int32_t* __restrict__ kt) {
+  __shared__ uint32_t tq[32][33], tk[32][33];
+  const int64_t t0 = (int64_t)blockIdx.x * 32;
+  const int h0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int64_t t = t0 + r;
+    const int h = h0 + threadIdx.x;
+    if (t < N && h < H) {
+      tq[r][threadIdx.x] = q[t * H + h];
+      tk[r][threadIdx.x] = k[t * H + h];
+    }
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int h = h0 + r;
+    const int64_t t = t0 + threadIdx.x;
+    if (t < N && h < H) {
+      qt[(int64_t)h * N + t] = (int32_t)tq[threadIdx.x][r];
+      kt[(int64_t)h * N + t] = (int32_t)tk[threadIdx.x][r];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ matching
+// grid = (work items, heads); a work item is kFwdBand consecutive diagonals of one
+// sequence; every warp of the CTA walks its own 256 diagonals independently.
+__global__ void __launch_bounds__(kFwdWarps * 32)
+    hard_match_kernel(Plan plan, const int32_t* __restrict__ qsym,
+                      const int32_t* __restrict__ ksym, int64_t sym_seq_stride,
+                      int64_t sym_head_stride, int H, int W,
+                      unsigned long long* __restrict__ best) {
+  int seq, local;
+  if (!find_item(plan, blockIdx.x, &seq, &local)) return;
+  const int h = blockIdx.y;
+  const int start = plan.seg_start[seq];
+  const int len = plan.seg_len[seq];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int delta0 = 1 + local * kFwdBand + warp * (32 * kFwdPerLane);
+  if (delta0 > len - 1) return;
+  const bool dense = plan.cu_seqlens == nullptr;
+  const int64_t sym_base =
+      (int64_t)seq * sym_seq_stride + (int64_t)h * sym_head_stride + (dense ? 0 : start);
+  const int32_t* __restrict__ q = qsym + sym_base;
+  const int32_t* __restrict__ k = ksym + sym_base;
+
+  int run[kFwdPerLane];
+#pragma unroll
+  for (int r = 0; r < kFwdPerLane; ++r) run[r] = 0;
+
+  for (int i = delta0; i < len; ++i) {
+    const int qi = __ldg(q + i);
+    int best_len = 0, best_route = 0;
+    const int jbase = i - delta0 - lane;
+#pragma unroll
+    for (int r = 0; r < kFwdPerLane; ++r) {
+      const int j = jbase - r * 32;
+      int l = 0;
+      if (j >= 0) {
+        const int kj = __ldg(k + j);
+        l = (kj == qi) ? min(run[r] + 1, W) : 0;
+      }
+      run[r] = l;
+      if (l > best_len) {  // r ascending = route descending: strict > keeps the latest
+        best_len = l;
+        best_route = j + 1;
+      }
+    }
+    const int row_len = __reduce_max_sync(0xffffffffu, best_len);
+    if (row_len > 0) {
+      const int row_route =
+          __reduce_max_sync(0xffffffffu, best_len == row_len ? best_route : 0);
+      if (lane == 0) {
+        const unsigned long long key =
+            ((unsigned long long)(unsigned)row_len << 32) | (unsigned)row_route;
+        unsigned long long* slot = best + ((int64_t)(start + i) * H + h);
+        if (*reinterpret_cast<volatile unsigned long long*>(slot) < key) atomicMax(slot, key);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------- gather
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <>
+__device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float x) { return __float2half(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
+  return __float2bfloat16(x);
+}
+
+// One thread per (token, head, chunk of kChunk value components).
+template <typename T>
+__global__ void gather_output_kernel(Plan plan, const unsigned long long* __restrict__ best,
+                                     const T* __restrict__ v, int64_t N, int H, int Hv, int Dv,
+                                     T* __restrict__ out, int32_t* __restrict__ route_token) {
+  constexpr int kChunk = 8;
+  const int chunks = (Dv + kChunk - 1) / kChunk;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= N * H * chunks) return;
+  const int c = (int)(idx % chunks);
+  const int64_t th = idx / chunks;
+  const int64_t token = th / H;
+  const int h = (int)(th - token * H);
+  const int route = (int)(best[th] & 0xffffffffull);
+  int start = 0, len = 0;
+  int64_t src_token = -1;
+  if (route > 0 && find_segment(plan, token, &start, &len) >= 0) src_token = (int64_t)start + route;
+  if (c == 0 && route_token) route_token[th] = (int32_t)src_token;
+  T* o = out + th * Dv;
+  const int d0 = c * kChunk, d1 = min(Dv, d0 + kChunk);
+  if (src_token < 0) {
+    for (int d = d0; d < d1; ++d) o[d] = from_float<T>(0.0f);
+  } else {
+    const T* src = v + (src_token * Hv + h / (H / Hv)) * Dv;
+    for (int d = d0; d < d1; ++d) o[d] = from_float<T>(positive<T>(src[d]) ? 1.0f : -1.0f);
+  }
+}
+
+__global__ void inference_finish_kernel(Plan plan, const unsigned long long* __restrict__ best,
+                                        const float* __restrict__ payload, int64_t N, int H,
+                                        int Hp, int Dp, float* __restrict__ out,
+                                        int64_t* __restrict__ matched_end) {
+  const int64_t th = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (th >= N * H) return;
+  const int64_t token = th / H;
+  const int h = (int)(th - token * H);
+  const int route = (int)(best[th] & 0xffffffffull);
+  int start = 0, len = 0;
+  const bool hit = route > 0 && find_segment(plan, token, &start, &len) >= 0;
+  matched_end[th] = hit ? (int64_t)route - 1 : -1;
+  if (out) {
+    float* o = out + th * Dp;
+    if (hit) {
+      const float* src = payload + (((int64_t)start + route) * Hp + h / (H / Hp)) * Dp;
+      for (int d = 0; d < Dp; ++d) o[d] = src[d];
+    } else {
+      for (int d = 0; d < Dp; ++d) o[d] = 0.0f;
+    }
+  }
+}
+
+}  // namespace
+
+int launch_pack_symbols(const void* q, const void* k, int dtype, int64_t N, int H, int D,
+                        int dense, int64_t uniform_len, int32_t* pq, int32_t* pk,
+                        cudaStream_t stream) {
+  ProfileScope prof("pack_symbols", stream);
+  const int threads = 256;
+  const int64_t blocks = (N * H + threads - 1) / threads;
+  if (dtype == ROSA_B200_F32)
+    pack_symbols_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
+        (const float*)q, (const float*)k, N, H, D, dense, uniform_len, pq, pk);
+  else if (dtype == ROSA_B200_F16)
+    pack_symbols_kernel<__half><<<(unsigned)blocks, threads, 0, stream>>>(
+        (const __half*)q, (const __half*)k, N, H, D, dense, uniform_len, pq, pk);
+  else
+    pack_symbols_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, N, H, D, dense, uniform_len, pq, pk);
+  ROSA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int launch_transpose_symbols(const uint32_t* q, const uint32_t* k, int64_t N, int H, int32_t* qt,
+                             int32_t* kt, cudaStream_t stream) {
+  ProfileScope prof("transpose_symbols", stream);
+  dim3 grid((unsigned)((N + 31) / 32), (unsigned)((H + 31) / 32)), block(32, 8);
+  transpose_symbols_kernel<<<grid, block, 0, stream>>>(q, k, N, H, qt, kt);
+  ROSA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int launch_hard_match(const FwdArgs& a, int items_upper, cudaStream_t stream) {
+  if (items_upper <= 0) return 0;
+  ProfileScope prof("hard_match", stream);
+  dim3 grid((unsigned)items_upper, (unsigned)a.H);
+  hard_match_kernel<<<grid, kFwdWarps * 32, 0, stream>>>(a.plan, a.packed_q, a.packed_k,
+                                                        a.sym_seq_stride, a.sym_head_stride, a.H,
+                                                        a.W, a.best);
+  ROSA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int launch_gather_output(const FwdArgs& a, cudaStream_t stream) {
+  ProfileScope prof("gather_output", stream);
+  const int chunks = (a.Dv + 7) / 8;
+  const int threads = 256;
+  const int64_t total = a.N * a.H * chunks;
+  const int64_t blocks = (total + threads - 1) / threads;
+  if (a.dtype == ROSA_B200_F32)
+    gather_output_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
+        a.plan, a.best, (const float*)a.v, a.N, a.H, a.Hv, a.Dv, (float*)a.out, a.route_token);
+  else if (a.dtype == ROSA_B200_F16)
+    gather_output_kernel<__half><<<(unsigned)blocks, threads, 0, stream>>>(
+        a.plan, a.best, (const __half*)a.v, a.N, a.H, a.Hv, a.Dv, (__half*)a.out, a.route_token);
+  else
+    gather_output_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
+        a.plan, a.best, (const __nv_bfloat16*)a.v, a.N, a.H, a.Hv, a.Dv, (__nv_bfloat16*)a.out,
+        a.route_token);
+  ROSA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int launch_inference_finish(const Plan& plan, const unsigned long long* best, const float* payload,
+                            int64_t N, int H, int Hp, int Dp, float* out, int64_t* matched_end,
+                            cudaStream_t stream) {
+  ProfileScope prof("inference_finish", stream);
+  const int threads = 256;
+  const int64_t blocks = (N * H + threads - 1) / threads;
+  inference_finish_kernel<<<(unsigned)blocks, threads, 0, stream>>>(plan, best, payload, N, H, Hp,
+                                                                   Dp, out, matched_end);
+  ROSA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace rosa

@@ -1,0 +1,56 @@
+"""Shared helpers of the GPU parity tests (seeded inputs, oracle calls, error metrics)."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from oracle import rosa_oracle as orc
+
+TORCH_DTYPES = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16,
+                "float64": torch.float32}
+
+
+def nonzero_randn(shape, seed, dtype=torch.float32):
+    """|x| >= 0.2 so that signs are unambiguous in every dtype (same construction as the
+    reference tests, tests/test_soft_cuda.py:18-26)."""
+    g = torch.Generator().manual_seed(seed)
+    values = torch.randn(shape, dtype=torch.float32, generator=g)
+    values = values.sign().masked_fill(values == 0, 1) * (values.abs() + 0.2)
+    return values.to(dtype)
+
+
+def repeated_stream_logits(n_tokens, heads, bits, seed, repeat_prob=0.3, seg=(4, 40), scale=0.7):
+    """+-scale logits of a token stream over alphabet 2**bits in which segments repeat, so hard
+    matches are long (the long-match stress construction)."""
+    rng = np.random.default_rng(seed)
+    out = np.empty((n_tokens, heads, bits), np.float32)
+    for h in range(heads):
+        toks = []
+        while len(toks) < n_tokens:
+            length = int(rng.integers(seg[0], seg[1] + 1))
+            if toks and rng.random() < repeat_prob and len(toks) > length:
+                start = int(rng.integers(0, len(toks) - length + 1))
+                toks.extend(toks[start:start + length])
+            else:
+                toks.extend(rng.integers(0, 1 << bits, size=length).tolist())
+        toks = np.array(toks[:n_tokens])
+        for d in range(bits):
+            out[:, h, d] = np.where((toks >> d) & 1, scale, -scale)
+    return torch.from_numpy(out)
+
+
+def normalised_error(mine, ref):
+    ref = np.asarray(ref, dtype=np.float64)
+    mine = np.asarray(mine, dtype=np.float64).reshape(ref.shape)
+    scale = max(float(np.abs(ref).max()), 1e-30)
+    return float(np.abs(mine - ref).max()) / scale
+
+
+def oracle_grads(q, k, v, go, cu, W, scale, p, m, seed, mask=7, batch_offset=0):
+    f = lambda t: t.detach().float().cpu().numpy()
+    return orc.surrogate_vjp(f(q), f(k), f(v), f(go), cu, W, scale, p, m, seed, batch_offset, mask)
+
+
+def oracle_forward(q, k, v, cu, W):
+    f = lambda t: t.detach().float().cpu().numpy()
+    return orc.hard_forward(f(q), f(k), f(v), cu, W)

@@ -1,0 +1,121 @@
+"""CPU-side checks: the C ABI library loads and exports every declared symbol, the package
+surface matches the reference's, the host-side contract raises the reference's errors."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from rosa_soft_b200 import cabi
+    header = open(os.path.join(ROOT, "include", "rosa_soft_b200.h")).read()
+    declared = set(re.findall(r"ROSA_B200_API[^;(]*?\b(rosa_b200_\w+)\s*\(", header))
+    assert declared == set(cabi.EXPORTED_SYMBOLS)
+    lib = ctypes.CDLL(cabi.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert cabi.load().rosa_b200_abi_version() == 1
+
+
+def test_workspace_sizes_are_pure_functions_of_shapes():
+    from rosa_soft_b200 import cabi
+    lib = cabi.load()
+    a = lib.rosa_b200_surrogate_vjp_workspace_bytes(2 * 1024, 64, 8, 16, 8, 2, 1024, 128, 7)
+    b = lib.rosa_b200_surrogate_vjp_workspace_bytes(2 * 1024, 64, 8, 16, 8, 2, 1024, 128, 7)
+    assert a == b and a > 0
+    # masked-off gradients need no partial buffers
+    assert lib.rosa_b200_surrogate_vjp_workspace_bytes(2 * 1024, 64, 8, 16, 8, 2, 1024, 128, 4) < a
+    # the packed bound grows with the token count, never reads offsets
+    small = lib.rosa_b200_surrogate_vjp_workspace_bytes(4096, 4, 8, 2, 8, 16, 0, 64, 7)
+    large = lib.rosa_b200_surrogate_vjp_workspace_bytes(8192, 4, 8, 2, 8, 16, 0, 64, 7)
+    assert 0 < small < large
+
+
+def test_argument_errors_without_a_gpu():
+    from rosa_soft_b200 import cabi
+    lib = cabi.load()
+    rc = lib.rosa_b200_hard_forward(None, None, None, 0, 8, 2, 40, 1, 3, None, 1, 8, 4, None, None,
+                                    None, None, None, 0, None)
+    assert rc != 0 and "bit dimension must be in [1, 32]" in cabi.last_error()
+    rc = lib.rosa_b200_hard_forward(None, None, None, 0, 8, 3, 4, 2, 3, None, 1, 8, 4, None, None,
+                                    None, None, None, 0, None)
+    assert rc != 0 and "divisible by value heads" in cabi.last_error()
+
+
+def test_package_surface_and_schemas():
+    import rosa_soft_b200 as pkg
+    caps = pkg.BUILD_CAPABILITIES
+    assert (caps.variant, caps.compiled_extension, caps.rosa_soft_cuda) == ("cuda", True, True)
+    with pytest.raises(Exception):
+        caps.variant = "x"
+    for name in ("rosa_soft", "rosa_soft_varlen", "BUILD_CAPABILITIES", "__version__"):
+        assert name in pkg.__all__
+    want = {
+        "hard_forward": "rosa_soft::hard_forward(Tensor query, Tensor key, Tensor value, int max_suffix_length) -> (Tensor output, Tensor packed_query_symbols, Tensor packed_key_symbols)",
+        "hard_forward_varlen": "rosa_soft::hard_forward_varlen(Tensor query, Tensor key, Tensor value, Tensor cu_seqlens, int max_suffix_length) -> (Tensor output, Tensor packed_query_symbols, Tensor packed_key_symbols)",
+        "surrogate_vjp_masked": "rosa_soft::surrogate_vjp_masked(Tensor query, Tensor key, Tensor value, Tensor grad_output, Tensor packed_query_symbols, Tensor packed_key_symbols, Tensor dropout_seed, int max_suffix_length, float scale, float dropout_p, float mismatch_scale, int gradient_mask) -> (Tensor grad_query, Tensor grad_key, Tensor grad_value)",
+        "surrogate_vjp_varlen_masked": "rosa_soft::surrogate_vjp_varlen_masked(Tensor query, Tensor key, Tensor value, Tensor cu_seqlens, Tensor grad_output, Tensor packed_query_symbols, Tensor packed_key_symbols, Tensor dropout_seed, int max_suffix_length, float scale, float dropout_p, float mismatch_scale, int gradient_mask) -> (Tensor grad_query, Tensor grad_key, Tensor grad_value)",
+    }
+    for op, schema in want.items():
+        assert str(getattr(torch.ops.rosa_soft, op).default._schema) == schema
+        assert torch._C._dispatch_has_kernel_for_dispatch_key(f"rosa_soft::{op}", "CUDA")
+        assert not torch._C._dispatch_has_kernel_for_dispatch_key(f"rosa_soft::{op}", "CPU")
+
+
+def test_no_cpu_fallback():
+    import rosa_soft_b200 as pkg
+    q = torch.randn(1, 4, 1, 2)
+    with pytest.raises(ValueError, match="requires CUDA tensors"):
+        pkg.rosa_soft(q, q, q)
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        torch.ops.rosa_soft.hard_forward(q, q, q, 2)
+
+
+def test_validation_matrix():
+    from rosa_soft_b200 import soft_contract as sc
+    q = torch.randn(2, 6, 4, 3)
+    v = torch.randn(2, 6, 2, 5)
+    assert sc.validate_rosa_soft_inputs(q, q, v, 32, 1.0, 0.0, 3.0) == 6
+    assert sc.validate_rosa_soft_inputs(q, q, v, 4, 1.0, 0.0, 3.0) == 4
+    cases = [
+        (dict(max_suffix_length=True), TypeError, "must be an integer"),
+        (dict(max_suffix_length=1.5), TypeError, "must be an integer"),
+        (dict(max_suffix_length=0), ValueError, ">= 1"),
+        (dict(scale=float("inf")), ValueError, "scale must be finite"),
+        (dict(scale=True), ValueError, "scale must be finite"),
+        (dict(dropout_p=1.0), ValueError, "dropout_p must be finite"),
+        (dict(dropout_p=-0.1), ValueError, "dropout_p must be finite"),
+        (dict(mismatch_scale=0.0), ValueError, "mismatch_scale must be finite"),
+    ]
+    base = dict(max_suffix_length=8, scale=1.0, dropout_p=0.0, mismatch_scale=3.0)
+    for override, exc, text in cases:
+        kw = {**base, **override}
+        with pytest.raises(exc, match=text):
+            sc.validate_rosa_soft_inputs(q, q, v, kw["max_suffix_length"], kw["scale"],
+                                         kw["dropout_p"], kw["mismatch_scale"])
+    with pytest.raises(ValueError, match="divisible by value heads"):
+        sc.validate_rosa_soft_inputs(q, q, torch.randn(2, 6, 3, 5), 8, 1.0, 0.0, 3.0)
+    with pytest.raises(ValueError, match=r"in \[1, 32\]"):
+        sc.validate_rosa_soft_inputs(torch.randn(1, 2, 1, 33), torch.randn(1, 2, 1, 33),
+                                     torch.randn(1, 2, 1, 1), 8, 1.0, 0.0, 3.0)
+    with pytest.raises(ValueError, match="same dtype"):
+        sc.validate_rosa_soft_inputs(q, q.double(), v, 8, 1.0, 0.0, 3.0)
+    qv, vv = torch.randn(10, 2, 3), torch.randn(10, 1, 2)
+    good = torch.tensor([0, 4, 10], dtype=torch.int32)
+    assert sc.validate_rosa_soft_varlen_inputs(qv, qv, vv, good, 64, 1.0, 0.0, 3.0) == 10
+    for bad, text in ((torch.tensor([1, 4, 10], dtype=torch.int32), "start at zero"),
+                      (torch.tensor([0, 4, 9], dtype=torch.int32), "end at the packed token count"),
+                      (torch.tensor([0, 6, 4, 10], dtype=torch.int32), "nondecreasing"),
+                      (torch.tensor([0, 10], dtype=torch.int64), "dtype int32")):
+        with pytest.raises(ValueError, match=text):
+            sc.validate_rosa_soft_varlen_inputs(qv, qv, vv, bad, 8, 1.0, 0.0, 3.0)
+    with pytest.raises(ValueError, match="max_suffix_length \\* scale must fit"):
+        sc.validate_fp32_surrogate_scalars(1 << 20, 3e38, 0.0, 3.0)
+    seed = sc.make_dropout_seed(q, 0.0, True)
+    assert seed.numel() == 0 and seed.dtype == torch.int64
+    assert sc.make_dropout_seed(q, 0.5, False).numel() == 0
+    assert sc.make_dropout_seed(q, 0.5, True).shape == ()
