@@ -95,6 +95,9 @@ class ClockSampler:
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            deadline = time.time() + 3.0   # let the first sample arrive before timing starts
+            while not self.samples and time.time() < deadline:
+                time.sleep(0.02)
         except OSError:
             self.proc = None
         return self
