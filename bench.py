@@ -37,6 +37,9 @@ WORKLOADS = {
                dtype="bfloat16", gen="randn"),
     "c3": dict(B=1, T=8192, H=64, D=2, Hv=64, Dv=16, W=256, scale=1.0, p=0.0, m=3.0,
                dtype="bfloat16", gen="repeat"),
+    # a case small enough for a full-metric profiler capture whose scratch still exceeds L2
+    "profile": dict(B=1, T=4096, H=32, D=8, Hv=8, Dv=8, W=128, scale=1.0, p=0.1, m=3.0,
+                    dtype="bfloat16", gen="randn"),
     "small": dict(B=1, T=1024, H=8, D=8, Hv=2, Dv=8, W=128, scale=1.0, p=0.1, m=3.0,
                   dtype="bfloat16", gen="randn"),
 }

@@ -49,7 +49,7 @@ FwdLayout fwd_layout(int64_t N, int H, int64_t S, bool transposed_symbols) {
 
 struct VjpLayout {
   PlanLayout plan;
-  size_t vbits_off, ckpt_off, stat_off, rowstat_off, ring_off, dq_off, dk_off, dv_off;
+  size_t vbits_off, ckpt_off, keep_off, stat_off, rowstat_off, ring_off, dq_off, dk_off, dv_off;
   size_t ring_bytes;
   size_t bytes;
   int bands_per_item;
@@ -98,6 +98,8 @@ VjpLayout vjp_layout(int64_t N, int H, int D, int Hv, int Dv, int64_t S, int64_t
   off = align_up(off + (size_t)N * Hv * l.vwords * sizeof(uint32_t));
   l.ckpt_off = off;
   off = align_up(off + (size_t)cks * H * kVjpBand * sizeof(int2));
+  l.keep_off = off;
+  off = align_up(off + (size_t)cks * H * kVjpRows * kVjpWarps * sizeof(uint32_t));
   l.stat_off = off;
   off = align_up(off + (size_t)rows * H * sizeof(float4));
   l.rowstat_off = off;
@@ -296,6 +298,7 @@ ROSA_B200_API int rosa_b200_surrogate_vjp(const void* query, const void* key, co
   a.batch_offset = (uint32_t)dropout_batch_offset;
   a.head_offset = (uint32_t)dropout_head_offset;
   a.ckpt = reinterpret_cast<int2*>(ws + l.ckpt_off);
+  a.keepbits = reinterpret_cast<uint32_t*>(ws + l.keep_off);
   a.stat_part = reinterpret_cast<float4*>(ws + l.stat_off);
   a.rowstat = reinterpret_cast<float4*>(ws + l.rowstat_off);
   a.ring = reinterpret_cast<float*>(ws + l.ring_off);

@@ -155,23 +155,35 @@ __device__ __forceinline__ uint32_t avalanche(uint32_t s) {
   return s;
 }
 
+// The chain is route -> query position -> head -> batch -> seed low -> seed high.  The
+// first round depends on the route only, so callers hash it once per key column
+// (dropout_route_hash) and finish the chain per cell (dropout_keep_from_route).  The keep test
+// `float(st >> 8) * 2^-24 >= p` is evaluated exactly on integers: the 24-bit value and the
+// power-of-two scaling are exact in float32, so it equals `(st >> 8) >= ceil(p * 2^24)`.
 struct DropoutKey {
   uint32_t head_salted;   // head ^ salt
   uint32_t batch_salted;  // batch ^ salt
   uint32_t seed_lo;
   uint32_t seed_hi_salted;
-  float p;
+  uint32_t threshold;     // ceil(float32(p) * 2^24)
 };
 
-__device__ __forceinline__ bool dropout_keep(const DropoutKey& k, uint32_t route, uint32_t query) {
-  uint32_t st = avalanche(route ^ 0x68E31DA4u);
-  st = avalanche(st ^ query ^ 0xB5297A4Du);
+__device__ __forceinline__ uint32_t dropout_route_hash(uint32_t route) {
+  return avalanche(route ^ 0x68E31DA4u);
+}
+
+__device__ __forceinline__ bool dropout_keep_from_route(const DropoutKey& k, uint32_t route_hash,
+                                                        uint32_t query) {
+  uint32_t st = avalanche(route_hash ^ query ^ 0xB5297A4Du);
   st = avalanche(st ^ k.head_salted);
   st = avalanche(st ^ k.batch_salted);
   st = avalanche(st ^ k.seed_lo);
   st = avalanche(st ^ k.seed_hi_salted);
-  const float uniform = (float)(st >> 8) * (1.0f / 16777216.0f);
-  return uniform >= k.p;
+  return (st >> 8) >= k.threshold;
+}
+
+__device__ __forceinline__ bool dropout_keep(const DropoutKey& k, uint32_t route, uint32_t query) {
+  return dropout_keep_from_route(k, dropout_route_hash(route), query);
 }
 
 __device__ __forceinline__ DropoutKey make_dropout_key(uint32_t head, uint32_t batch,
@@ -182,7 +194,7 @@ __device__ __forceinline__ DropoutKey make_dropout_key(uint32_t head, uint32_t b
   k.batch_salted = batch ^ 0xA511E9B3u;
   k.seed_lo = (uint32_t)(seed & 0xFFFFFFFFull);
   k.seed_hi_salted = (uint32_t)(seed >> 32) ^ 0x9E3779B9u;
-  k.p = p;
+  k.threshold = (uint32_t)ceil((double)p * 16777216.0);
   return k;
 }
 
@@ -279,6 +291,7 @@ struct VjpArgs {
   uint32_t batch_offset, head_offset;
   // scratch
   int2* ckpt;                      // (S bits, window mismatch sum) per (block, diagonal)
+  uint32_t* keepbits;              // dropout keep ballots: [ckpt block][row][warp]
   float4* stat_part;               // (max, sum, weighted sum) per (item, row)
   float4* rowstat;                 // [H][N] (max, 1/Z, E, log i)
   float* ring;                     // [items][W+1][band] (0 when the window never closes)

@@ -117,7 +117,7 @@ __device__ __forceinline__ void build_ulut(const VjpArgs& a, const Item& it, int
         s += (nib >> b & 1) ? gv : -gv;
       }
     }
-    ulut[(r * 8 + g) * 16 + nib] = s;
+    ulut[(r * ngroups + g) * 16 + nib] = s;
   }
 }
 
@@ -129,7 +129,7 @@ __device__ __forceinline__ float route_utility(const VjpArgs& a, const Item& it,
   if (kSmallDv) {
     const uint32_t bits = __ldg(vb + route);
     float u = 0.0f;
-    for (int g = 0; g < ngroups; ++g) u += ulut[(r * 8 + g) * 16 + ((bits >> (4 * g)) & 15u)];
+    for (int g = 0; g < ngroups; ++g) u += ulut[(r * ngroups + g) * 16 + ((bits >> (4 * g)) & 15u)];
     return u;
   } else {
     const int64_t base = (((int64_t)it.start + i) * a.H + it.h) * a.Dv;
@@ -146,38 +146,167 @@ __device__ __forceinline__ float route_utility(const VjpArgs& a, const Item& it,
   }
 }
 
-// shared-memory carve-up common to both sweeps (float units)
+// Sum of eight per-lane values across a warp in 9 shuffles instead of 40: each step
+// exchanges half of the remaining values with the partner lane.  On return every lane
+// holds the warp total of value index ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 +
+// ((lane >> 2) & 1).
+__device__ __forceinline__ float warp_reduce8(const float (&v)[8], int lane) {
+  const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
+  float a[4], b[2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float send = h16 ? v[i] : v[i + 4];
+    const float keep = h16 ? v[i + 4] : v[i];
+    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float send = h8 ? a[i] : a[i + 2];
+    const float keep = h8 ? a[i + 2] : a[i];
+    b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+  float c = (h4 ? b[1] : b[0]) + __shfl_xor_sync(0xffffffffu, h4 ? b[0] : b[1], 4);
+  c += __shfl_xor_sync(0xffffffffu, c, 2);
+  c += __shfl_xor_sync(0xffffffffu, c, 1);
+  return c;
+}
+
+// ------------------------------------------------------------ block tables
+// Every row block of a band touches the query rows [i0, i0 + nrows) and the key columns
+// [jwin0, jwin0 + nrows + kVjpBand - 1), jwin0 = i0 - dmax.  Thread `tid` (diagonal
+// dmin + tid) on block row r sits on column index c = r + kVjpBand - 1 - tid of that
+// window, so everything a cell needs is one shared-memory read away and the inner loops
+// carry no global loads, no bounds branches and no 64-bit address arithmetic.
+constexpr int kWinCols = kVjpRows + kVjpBand;  // window columns (one spare)
+
 struct SweepSmem {
-  float* glut;    // [33] gate per mismatch count
-  int* s_q;       // [kVjpRows] query symbols of the block rows
-  float4* rstat;  // [kVjpRows] (max, 1/Z, E, log i); sweep 1 only uses .w
-  float4* wstat;  // [kVjpRows * kVjpWarps] per-warp online-softmax partials (sweep 1)
-  float* ulut;    // [kVjpRows * 8 * 16]
+  float4* rstat;     // [kVjpRows] (max, 1/Z, E, log i); sweep 1 only uses .w
+  float4* wstat;     // [kVjpRows * kVjpWarps] per-warp softmax partials (sweep 1)
+  uint32_t* s_keep;  // [kVjpRows * kVjpWarps] dropout keep ballots of the block (sweep 2)
+  float* ulut;       // [kVjpRows * ngroups * 16] nibble tables of gO . sign(V)
+  float* glut;       // [64] gate per mismatch count
+  int* s_q;          // [kVjpRows] query symbols of the block rows
+  int* s_qold;       // [kVjpRows] query symbols W + 1 rows earlier (window tail)
+  int* s_k;          // [kWinCols] key symbols of the column window
+  int* s_kold;       // [kWinCols] key symbols W + 1 columns earlier
+  uint32_t* s_vb;    // [kWinCols] value sign bits of route j + 1 (Dv <= 32)
+  uint32_t* s_h1;    // [kWinCols] first dropout hash round of route j + 1 (sweep 1)
+  float* rest;       // first float after the common part
 };
 
-constexpr int kSweepCommonFloats =
-    64 + kVjpRows + 4 * kVjpRows + 4 * kVjpRows * kVjpWarps + kVjpRows * 8 * 16;
+__host__ __device__ inline int sweep_common_floats(int ngroups) {
+  return 4 * kVjpRows + 4 * kVjpRows * kVjpWarps + kVjpRows * ngroups * 16 + 64 + 2 * kVjpRows +
+         4 * kWinCols;
+}
 
-__device__ __forceinline__ SweepSmem carve_common(float* base) {
+__device__ __forceinline__ SweepSmem carve_common(float* base, int ngroups) {
   SweepSmem s;
   s.rstat = reinterpret_cast<float4*>(base);
   s.wstat = s.rstat + kVjpRows;
+  s.s_keep = reinterpret_cast<uint32_t*>(s.wstat);  // the two are never live together
   float* f = reinterpret_cast<float*>(s.wstat + kVjpRows * kVjpWarps);
-  s.ulut = f;
-  f += kVjpRows * 8 * 16;
-  s.glut = f;
-  f += 64;
-  s.s_q = reinterpret_cast<int*>(f);
+  s.ulut = f;            f += kVjpRows * ngroups * 16;
+  s.glut = f;            f += 64;
+  s.s_q = reinterpret_cast<int*>(f);        f += kVjpRows;
+  s.s_qold = reinterpret_cast<int*>(f);     f += kVjpRows;
+  s.s_k = reinterpret_cast<int*>(f);        f += kWinCols;
+  s.s_kold = reinterpret_cast<int*>(f);     f += kWinCols;
+  s.s_vb = reinterpret_cast<uint32_t*>(f);  f += kWinCols;
+  s.s_h1 = reinterpret_cast<uint32_t*>(f);  f += kWinCols;
+  s.rest = f;
   return s;
 }
 
-// ------------------------------------------------------------------- sweep 1
+// Fills the symbol / value-bit / hash windows of one block.  Out-of-range entries are 0.
 template <bool kSmallDv>
+__device__ __forceinline__ void fill_block_windows(const SweepSmem& sm, const Item& it,
+                                                   const int32_t* __restrict__ q,
+                                                   const int32_t* __restrict__ k,
+                                                   const uint32_t* __restrict__ vb, int i0,
+                                                   int nrows, int jwin0, bool windowed, int W,
+                                                   bool want_hash) {
+  const int tid = threadIdx.x;
+  if (tid < nrows) {
+    const int i = i0 + tid;
+    sm.s_q[tid] = __ldg(q + i);
+    sm.s_qold[tid] = (windowed && i - W - 1 >= 0) ? __ldg(q + i - W - 1) : 0;
+  }
+  for (int c = tid; c < nrows + kVjpBand - 1; c += kVjpBand) {
+    const int j = jwin0 + c;
+    const bool in = j >= 0 && j < it.len - 1;  // a key column of some cell
+    sm.s_k[c] = in ? __ldg(k + j) : 0;
+    const int jo = j - W - 1;
+    sm.s_kold[c] = (windowed && jo >= 0 && jo < it.len) ? __ldg(k + jo) : 0;
+    if (kSmallDv) sm.s_vb[c] = in ? __ldg(vb + j + 1) : 0u;
+    if (want_hash) sm.s_h1[c] = dropout_route_hash((uint32_t)(j + 1));
+  }
+}
+
+// Branch-free forward step of one diagonal: gate, window product, evidence.
+// Inactive cells (before the diagonal starts) leave S and hs at zero.
+__device__ __forceinline__ float forward_cell(float& S, int& hs, bool act, int qi, int kj,
+                                              int qold, int kold, int j, const float* glut,
+                                              bool windowed, int W, float neg_md) {
+  const int ham = __popc(qi ^ kj);
+  const float x = glut[ham];
+  float P = 0.0f;
+  if (windowed) {
+    hs += act ? ham : 0;
+    hs -= (j > W) ? __popc(qold ^ kold) : 0;
+    const float pw = __expf(neg_md * (float)hs);
+    P = (j >= W) ? pw : 0.0f;
+  }
+  const float Sn = x * (1.0f + S) - P;
+  S = act ? Sn : 0.0f;
+  return P;
+}
+
+template <bool kSmallDv>
+__device__ __forceinline__ float cell_utility(const VjpArgs& a, const Item& it,
+                                              const SweepSmem& sm,
+                                              const uint32_t* __restrict__ vb, bool act, int i,
+                                              int j, int r, int c, int ngroups) {
+  if (kSmallDv) {
+    const uint32_t bits = sm.s_vb[c];
+    const float* lut = sm.ulut + r * ngroups * 16;
+    float u = 0.0f;
+    for (int g = 0; g < ngroups; ++g) u += lut[g * 16 + ((bits >> (4 * g)) & 15u)];
+    return u;
+  } else {
+    return act ? route_utility<false>(a, it, vb, i, r, j + 1, ngroups, sm.ulut) : 0.0f;
+  }
+}
+
+// Work item of a 1-D grid: heads vary fastest so that the longest bands of all heads are
+// scheduled first and the tail of the launch consists of the shortest bands.
+__device__ __forceinline__ bool load_item_1d(const VjpArgs& a, Item* o) {
+  const int slot = blockIdx.x / a.H;
+  if (!find_item(a.plan, slot, &o->seq, &o->it)) return false;
+  o->h = blockIdx.x - slot * a.H;
+  o->start = a.plan.seg_start[o->seq];
+  o->len = a.plan.seg_len[o->seq];
+  o->nitems = a.plan.item_prefix[o->seq + 1] - a.plan.item_prefix[o->seq];
+  const int nbands = (int)vjp_bands(o->len);
+  o->w_begin = o->it * a.bands_per_item;
+  o->w_end = min(nbands, o->w_begin + a.bands_per_item);
+  o->rowslot = a.plan.row_prefix[o->seq] * a.H +
+               ((int64_t)o->h * o->nitems + o->it) * (int64_t)o->len;
+  o->ck_base = a.plan.ck_prefix[o->seq] * a.H + (int64_t)o->h * vjp_ck_count(o->len);
+  o->item_linear = (int64_t)a.plan.item_prefix[o->seq] * a.H + (int64_t)o->h * o->nitems + o->it;
+  return true;
+}
+
+// ------------------------------------------------------------------- sweep 1
+// kFixedRef: the row reference of the online softmax is the analytic upper bound of the
+// logits (valid while scale * c * (sqrt(1 + W) - 1) stays far inside the float exponent
+// range), so no maximum has to be reduced and four rows share one transposing reduction.
+template <bool kSmallDv, bool kFixedRef>
 __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
   extern __shared__ float4 smem_raw[];
-  SweepSmem sm = carve_common(reinterpret_cast<float*>(smem_raw));
+  const int ngroups = kSmallDv ? (a.Dv + 3) / 4 : 0;
+  SweepSmem sm = carve_common(reinterpret_cast<float*>(smem_raw), ngroups);
   Item it;
-  if (!load_item(a, &it)) return;
+  if (!load_item_1d(a, &it)) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool dense = a.plan.cu_seqlens == nullptr;
   const int64_t sym_base = (int64_t)it.seq * a.sym_seq_stride + (int64_t)it.h * a.sym_head_stride +
@@ -186,16 +315,19 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
   const int32_t* __restrict__ k = a.ksym + sym_base;
   const int vh = it.h / a.group;
   const uint32_t* __restrict__ vb = a.vbits + ((int64_t)vh * a.N + it.start) * a.vwords;
-  const int ngroups = kSmallDv ? (a.Dv + 3) / 4 : 0;
+  const int W = a.W;
+  const float scale = a.scale, inv_keep = a.inv_keep;
   const float neg_md = -a.mismatch_scale / (float)a.D;
-  const bool windowed = a.W <= it.len - 2;
+  const bool windowed = W <= it.len - 2;
   const bool use_dropout = a.dropout_p > 0.0f;
   const DropoutKey dkey = make_dropout_key((uint32_t)it.h + a.head_offset,
                                            (uint32_t)it.seq + a.batch_offset, a.seed, a.dropout_p);
+  const float ref_top = scale * kSqrtScale * (sqrtf(1.0f + (float)W) - 1.0f);
   if (tid <= a.D) sm.glut[tid] = expf(neg_md * (float)tid);
 
   for (int w = it.w_begin; w < it.w_end; ++w) {
     const int dmin = 1 + w * kVjpBand;
+    const int dmax = dmin + kVjpBand - 1;
     const int delta = dmin + tid;
     const bool valid = delta <= it.len - 1;
     float S = 0.0f;
@@ -205,49 +337,93 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
     for (int rb = rb_lo; rb <= rb_hi; ++rb) {
       const int i0 = max(rb * kVjpRows, dmin), i1 = min(rb * kVjpRows + kVjpRows - 1, it.len - 1);
       const int nrows = i1 - i0 + 1;
+      const int jwin0 = i0 - dmax;
+      const int64_t ck_idx = ck_band + (rb - rb_lo);
       __syncthreads();
-      if (tid < nrows) {
-        sm.s_q[tid] = __ldg(q + i0 + tid);
-        sm.rstat[tid].w = logf((float)(i0 + tid));
-      }
+      fill_block_windows<kSmallDv>(sm, it, q, k, vb, i0, nrows, jwin0, windowed, W, use_dropout);
+      if (tid < nrows) sm.rstat[tid].w = logf((float)(i0 + tid));
       if (kSmallDv) build_ulut(a, it, i0, nrows, ngroups, sm.ulut);
       __syncthreads();
-      a.ckpt[(ck_band + (rb - rb_lo)) * kVjpBand + tid] = make_int2(__float_as_int(S), hs);
+      a.ckpt[ck_idx * kVjpBand + tid] = make_int2(__float_as_int(S), hs);
+      uint32_t* keep_out = a.keepbits + (ck_idx * kVjpRows) * kVjpWarps + warp;
+      // first row of the block on which this diagonal exists
+      const int r_first = valid ? max(0, delta - i0) : nrows;
+      const int cbase = kVjpBand - 1 - tid;   // column window index on block row 0
+      const int jbase = i0 - delta;           // key column on block row 0
 
-      for (int r = 0; r < nrows; ++r) {
-        const int i = i0 + r;
-        const int j = i - delta;
-        const bool act = valid && j >= 0;
-        float logit = -CUDART_INF_F, du = 0.0f;
-        if (act) {
-          const int qi = sm.s_q[r];
-          const int ham = __popc(qi ^ __ldg(k + j));
-          const float x = sm.glut[ham];
-          float P = 0.0f;
-          if (windowed) {
-            hs += ham;
-            if (j > a.W) hs -= __popc(__ldg(q + i - a.W - 1) ^ __ldg(k + j - a.W - 1));
-            if (j >= a.W) P = __expf(neg_md * (float)hs);
+      if (kFixedRef) {
+        for (int r0 = 0; r0 < nrows; r0 += 4) {
+          float v[8];
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            const int r = min(r0 + rr, nrows - 1);       // clamped: the tail repeats a row, masked
+            const bool act = r0 + rr < nrows && r >= r_first;
+            const int c = cbase + r, j = jbase + r, i = i0 + r;
+            if (r0 + rr < nrows)
+              forward_cell(S, hs, act, sm.s_q[r], sm.s_k[c], sm.s_qold[r], sm.s_kold[c], j,
+                           sm.glut, windowed, W, neg_md);
+            const float logit = kSqrtScale * (sqrtf(1.0f + S) - 1.0f) * scale - ref_top;
+            const float e = act ? __expf(logit) : 0.0f;   // the log i term cancels in the softmax
+            float du = cell_utility<kSmallDv>(a, it, sm, vb, act, i, j, r, c, ngroups);
+            if (use_dropout) {
+              const bool keep =
+                  act && dropout_keep_from_route(dkey, sm.s_h1[c], (uint32_t)i);
+              const uint32_t bits = __ballot_sync(0xffffffffu, keep);
+              if (lane == 0 && r0 + rr < nrows) keep_out[r * kVjpWarps] = bits;
+              du = keep ? du * inv_keep : 0.0f;
+            }
+            v[2 * rr] = e;
+            v[2 * rr + 1] = e * du;
           }
-          S = x * (1.0f + S) - P;
-          logit = kSqrtScale * (sqrtf(1.0f + S) - 1.0f) * a.scale - sm.rstat[r].w;
-          du = route_utility<kSmallDv>(a, it, vb, i, r, j + 1, ngroups, sm.ulut);
-          if (use_dropout)
-            du = dropout_keep(dkey, (uint32_t)(j + 1), (uint32_t)i) ? du * a.inv_keep : 0.0f;
+          const float total = warp_reduce8(v, lane);
+          if ((lane & 3) == 0) {
+            const int idx = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+            const int r = r0 + (idx >> 1);
+            if (r < nrows) {
+              float* dst = reinterpret_cast<float*>(sm.wstat + r * kVjpWarps + warp);
+              dst[1 + (idx & 1)] = total;
+            }
+          }
         }
-        const float mw = warp_max(logit);
-        const float e = act ? __expf(logit - mw) : 0.0f;
-        const float zw = warp_sum(e);
-        const float ew = warp_sum(e * du);
-        if (lane == 0) sm.wstat[r * kVjpWarps + warp] = make_float4(mw, zw, ew, 0.0f);
+      } else {
+        for (int r = 0; r < nrows; ++r) {
+          const bool act = r >= r_first;
+          const int c = cbase + r, j = jbase + r, i = i0 + r;
+          forward_cell(S, hs, act, sm.s_q[r], sm.s_k[c], sm.s_qold[r], sm.s_kold[c], j, sm.glut,
+                       windowed, W, neg_md);
+          const float logit = act ? kSqrtScale * (sqrtf(1.0f + S) - 1.0f) * scale - sm.rstat[r].w
+                                  : -CUDART_INF_F;
+          float du = cell_utility<kSmallDv>(a, it, sm, vb, act, i, j, r, c, ngroups);
+          if (use_dropout) {
+            const bool keep = act && dropout_keep_from_route(dkey, sm.s_h1[c], (uint32_t)i);
+            const uint32_t bits = __ballot_sync(0xffffffffu, keep);
+            if (lane == 0) keep_out[r * kVjpWarps] = bits;
+            du = keep ? du * inv_keep : 0.0f;
+          }
+          const float mw = warp_max(logit);
+          const float e = act ? __expf(logit - mw) : 0.0f;
+          const float zw = warp_sum(e);
+          const float ew = warp_sum(e * du);
+          if (lane == 0) sm.wstat[r * kVjpWarps + warp] = make_float4(mw, zw, ew, 0.0f);
+        }
       }
       __syncthreads();
       if (tid < nrows) {
         float m = -CUDART_INF_F, z = 0.0f, e = 0.0f;
+        if (kFixedRef) {
+          m = ref_top - sm.rstat[tid].w;
 #pragma unroll
-        for (int ww = 0; ww < kVjpWarps; ++ww) {
-          const float4 p = sm.wstat[tid * kVjpWarps + ww];
-          merge_stats(m, z, e, p.x, p.y, p.z);
+          for (int ww = 0; ww < kVjpWarps; ++ww) {
+            const float4 p = sm.wstat[tid * kVjpWarps + ww];
+            z += p.y;
+            e += p.z;
+          }
+        } else {
+#pragma unroll
+          for (int ww = 0; ww < kVjpWarps; ++ww) {
+            const float4 p = sm.wstat[tid * kVjpWarps + ww];
+            merge_stats(m, z, e, p.x, p.y, p.z);
+          }
         }
         const int64_t slot = it.rowslot + i0 + tid;
         if (w > it.w_begin) {
@@ -287,19 +463,41 @@ __global__ void vjp_rowstats_kernel(VjpArgs a) {
 }
 
 // ------------------------------------------------------------------- sweep 2
+// The per-cell work that does not depend on the adjoint chain: probability, dropout
+// multiplier, utility, dS.  Returns dS and writes p*d.  Inactive cells give zeros.
+template <bool kSmallDv>
+__device__ __forceinline__ float cell_adjoint_seed(const VjpArgs& a, const Item& it,
+                                                   const SweepSmem& sm,
+                                                   const uint32_t* __restrict__ vb, bool act,
+                                                   int i, int j, int r, int c, int lane, int warp,
+                                                   int ngroups, bool use_dropout, float scale,
+                                                   float inv_keep, float Sv, float* pd_out) {
+  const float4 st = sm.rstat[r];
+  const float sq = sqrtf(1.0f + Sv);
+  const float logit = kSqrtScale * (sq - 1.0f) * scale - st.w;
+  const float pr = act ? __expf(logit - st.x) * st.y : 0.0f;
+  float dmul = 1.0f;
+  if (use_dropout) dmul = (sm.s_keep[r * kVjpWarps + warp] >> lane & 1u) ? inv_keep : 0.0f;
+  const float u = cell_utility<kSmallDv>(a, it, sm, vb, act, i, j, r, c, ngroups);
+  const float pd = pr * dmul;
+  *pd_out = pd;
+  const float dlogit = pd * u - pr * st.z;
+  return scale * dlogit * (0.5f * kSqrtScale) * __frcp_rn(sq);
+}
+
 template <int DPAD, int DVPAD, bool kSmallDv>
-__global__ void __launch_bounds__(kVjpBand) vjp_sweep2_kernel(VjpArgs a) {
+__global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_kernel(VjpArgs a) {
   extern __shared__ float4 smem_raw[];
-  float* fbase = reinterpret_cast<float*>(smem_raw);
-  SweepSmem sm = carve_common(fbase);
-  float* Cbuf = fbase + kSweepCommonFloats;            // [kVjpRows][kVjpBand]; S, then C
+  const int ngroups = kSmallDv ? (a.Dv + 3) / 4 : 0;
+  SweepSmem sm = carve_common(reinterpret_cast<float*>(smem_raw), ngroups);
+  float* Cbuf = sm.rest;                               // [kVjpRows][kVjpBand]; S, then C
   float* Pbuf = Cbuf + kVjpRows * kVjpBand;            // [kVjpRows][kVjpBand]; P, then p*d
-  float* kz = Pbuf + kVjpRows * kVjpBand;              // [kVjpRows + kVjpBand][DPAD]
-  float* qz = kz + (kVjpRows + kVjpBand) * DPAD;       // [kVjpRows][DPAD]
+  float* kz = Pbuf + kVjpRows * kVjpBand;              // [kWinCols][DPAD]
+  float* qz = kz + kWinCols * DPAD;                    // [kVjpRows][DPAD]
   float* gob = qz + kVjpRows * DPAD;                   // [kVjpRows][DVPAD]
 
   Item it;
-  if (!load_item(a, &it)) return;
+  if (!load_item_1d(a, &it)) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool dense = a.plan.cu_seqlens == nullptr;
   const int64_t sym_base = (int64_t)it.seq * a.sym_seq_stride + (int64_t)it.h * a.sym_head_stride +
@@ -308,16 +506,15 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep2_kernel(VjpArgs a) {
   const int32_t* __restrict__ k = a.ksym + sym_base;
   const int vh = it.h / a.group;
   const uint32_t* __restrict__ vb = a.vbits + ((int64_t)vh * a.N + it.start) * a.vwords;
-  const int ngroups = kSmallDv ? (a.Dv + 3) / 4 : 0;
+  const int W = a.W, D = a.D, mask = a.mask, ring_slots = a.ring_slots;
+  const float scale = a.scale, inv_keep = a.inv_keep;
   const float neg_md = -a.mismatch_scale / (float)a.D;
-  const bool windowed = a.W <= it.len - 2;
+  const bool windowed = W <= it.len - 2;
   const bool use_dropout = a.dropout_p > 0.0f;
-  const DropoutKey dkey = make_dropout_key((uint32_t)it.h + a.head_offset,
-                                           (uint32_t)it.seq + a.batch_offset, a.seed, a.dropout_p);
   const float4* __restrict__ rowstat = a.rowstat + (int64_t)it.h * a.N + it.start;
-  float* ring = a.ring_slots ? a.ring + it.item_linear * (int64_t)a.ring_slots * kVjpBand + tid
-                             : nullptr;
-  if (tid <= a.D) sm.glut[tid] = expf(neg_md * (float)tid);
+  float* ring = ring_slots ? a.ring + it.item_linear * (int64_t)ring_slots * kVjpBand + tid
+                           : nullptr;
+  if (tid <= D) sm.glut[tid] = expf(neg_md * (float)tid);
 
   for (int w = it.w_begin; w < it.w_end; ++w) {
     const int dmin = 1 + w * kVjpBand;
@@ -330,83 +527,92 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep2_kernel(VjpArgs a) {
     float xnext = 0.0f;
     int live = 0;
     bool ring_dirty = false;
-    int slot = (valid && a.ring_slots) ? (it.len - 1 - delta) % a.ring_slots : 0;
+    int slot = (valid && ring_slots) ? (it.len - 1 - delta) % ring_slots : 0;
 
     for (int rb = rb_hi; rb >= rb_lo; --rb) {
       const int i0 = max(rb * kVjpRows, dmin), i1 = min(rb * kVjpRows + kVjpRows - 1, it.len - 1);
       const int nrows = i1 - i0 + 1;
       const int jwin0 = i0 - dmax;  // first key column of the block's column window
+      const int64_t ck_idx = ck_band + (rb - rb_lo);
       __syncthreads();
       // ---- block tables
-      if (tid < nrows) {
-        sm.s_q[tid] = __ldg(q + i0 + tid);
-        sm.rstat[tid] = rowstat[i0 + tid];
-      }
+      fill_block_windows<kSmallDv>(sm, it, q, k, vb, i0, nrows, jwin0, windowed, W, false);
+      if (tid < nrows) sm.rstat[tid] = rowstat[i0 + tid];
+      if (use_dropout && tid < nrows * kVjpWarps)
+        sm.s_keep[tid] = a.keepbits[(ck_idx * kVjpRows) * kVjpWarps + tid];
       if (kSmallDv) build_ulut(a, it, i0, nrows, ngroups, sm.ulut);
-      if (a.mask & 2)
+      const int2 ck = a.ckpt[ck_idx * kVjpBand + tid];
+      __syncthreads();
+      if (mask & 2)
         for (int e = tid; e < nrows * DPAD; e += kVjpBand) {
           const int r = e / DPAD, d = e - r * DPAD;
-          qz[e] = d < a.D ? ((__ldg(q + i0 + r) >> d & 1) ? 1.0f : -1.0f) : 0.0f;
+          qz[e] = d < D ? ((sm.s_q[r] >> d & 1) ? 1.0f : -1.0f) : 0.0f;
         }
-      if (a.mask & 1)
+      if (mask & 1)
         for (int e = tid; e < (nrows + kVjpBand - 1) * DPAD; e += kVjpBand) {
           const int c = e / DPAD, d = e - c * DPAD;
           const int j = jwin0 + c;
-          kz[e] = (d < a.D && j >= 0 && j < it.len) ? ((__ldg(k + j) >> d & 1) ? 1.0f : -1.0f)
-                                                    : 0.0f;
+          kz[e] = (d < D && j >= 0 && j < it.len - 1) ? ((sm.s_k[c] >> d & 1) ? 1.0f : -1.0f)
+                                                      : 0.0f;
         }
       // ---- phase A: forward recurrence of the block from its checkpoint
-      const int2 ck = a.ckpt[(ck_band + (rb - rb_lo)) * kVjpBand + tid];
       float S = __int_as_float(ck.x);
       int hs = ck.y;
-      __syncthreads();
+      const int r_first = valid ? max(0, delta - i0) : nrows;
+      const int cbase = kVjpBand - 1 - tid, jbase = i0 - delta;
+      bool has_p = false;
+#pragma unroll 4
       for (int r = 0; r < nrows; ++r) {
-        const int i = i0 + r;
-        const int j = i - delta;
-        float P = 0.0f, Sv = 0.0f;
-        if (valid && j >= 0) {
-          const int ham = __popc(sm.s_q[r] ^ __ldg(k + j));
-          if (windowed) {
-            hs += ham;
-            if (j > a.W) hs -= __popc(__ldg(q + i - a.W - 1) ^ __ldg(k + j - a.W - 1));
-            if (j >= a.W) P = __expf(neg_md * (float)hs);
-          }
-          S = sm.glut[ham] * (1.0f + S) - P;
-          Sv = S;
-        }
-        Cbuf[r * kVjpBand + tid] = Sv;
+        const int c = cbase + r;
+        const float P = forward_cell(S, hs, r >= r_first, sm.s_q[r], sm.s_k[c], sm.s_qold[r],
+                                     sm.s_kold[c], jbase + r, sm.glut, windowed, W, neg_md);
+        has_p |= P != 0.0f;
+        Cbuf[r * kVjpBand + tid] = S;
         Pbuf[r * kVjpBand + tid] = P;
       }
       // ---- phase B: adjoint recurrence, rows descending
-      for (int r = nrows - 1; r >= 0; --r) {
-        const int i = i0 + r;
-        const int j = i - delta;
-        const bool act = valid && j >= 0;
-        float Cv = 0.0f, pd = 0.0f, P = 0.0f;
-        double T = 0.0;
-        float x = 0.0f, Sv = 0.0f;
-        if (act) {
-          Sv = Cbuf[r * kVjpBand + tid];
-          P = Pbuf[r * kVjpBand + tid];
-          const float4 st = sm.rstat[r];
-          x = sm.glut[__popc(sm.s_q[r] ^ __ldg(k + j))];
-          const float sq = sqrtf(1.0f + Sv);
-          const float logit = kSqrtScale * (sq - 1.0f) * a.scale - st.w;
-          const float pr = __expf(logit - st.x) * st.y;
-          float dmul = 1.0f;
-          if (use_dropout)
-            dmul = dropout_keep(dkey, (uint32_t)(j + 1), (uint32_t)i) ? a.inv_keep : 0.0f;
-          const float u = route_utility<kSmallDv>(a, it, vb, i, r, j + 1, ngroups, sm.ulut);
-          pd = pr * dmul;
-          const float dlogit = pd * u - pr * st.z;
-          const float dS = a.scale * dlogit * kSqrtScale / (2.0f * sq);
-          Sbar = (double)dS + (double)xnext * Sbar;
-          T = Sbar * (double)P;
+      const bool warp_p = ring != nullptr && __any_sync(0xffffffffu, has_p);
+      if (!warp_p && live == 0) {
+        // no window product is alive in this warp: P = 0, T = 0, Y = 0, C = S * Sbar
+#pragma unroll 4
+        for (int r = nrows - 1; r >= 0; --r) {
+          const bool act = r >= r_first;
+          const int c = cbase + r;
+          const float Sv = Cbuf[r * kVjpBand + tid];
+          const float x = sm.glut[__popc(sm.s_q[r] ^ sm.s_k[c])];
+          float pd;
+          const float dS = cell_adjoint_seed<kSmallDv>(a, it, sm, vb, act, i0 + r, jbase + r, r, c,
+                                                       lane, warp, ngroups, use_dropout, scale,
+                                                       inv_keep, Sv, &pd);
+          Sbar = (double)dS + (double)xnext * Sbar;     // inactive: dS = 0 above the diagonal
+          Cbuf[r * kVjpBand + tid] = act ? (float)((double)Sv * Sbar) : 0.0f;
+          Pbuf[r * kVjpBand + tid] = pd;
+          xnext = x;
         }
-        if (ring != nullptr) {
+        if (valid && ring_slots) {  // keep the ring cursor in step with the rows walked
+          slot -= (nrows - r_first) % ring_slots;
+          if (slot < 0) slot += ring_slots;
+        }
+      } else {
+        for (int r = nrows - 1; r >= 0; --r) {
+          const bool act = r >= r_first;
+          const int c = cbase + r;
+          const float Sv = Cbuf[r * kVjpBand + tid];
+          const float P = Pbuf[r * kVjpBand + tid];
+          const float x = sm.glut[__popc(sm.s_q[r] ^ sm.s_k[c])];
+          float pd;
+          const float dS = cell_adjoint_seed<kSmallDv>(a, it, sm, vb, act, i0 + r, jbase + r, r, c,
+                                                       lane, warp, ngroups, use_dropout, scale,
+                                                       inv_keep, Sv, &pd);
+          float Cv = 0.0f;
+          double T = 0.0;
+          if (act) {
+            Sbar = (double)dS + (double)xnext * Sbar;
+            T = Sbar * (double)P;
+          }
           const bool any_p = __any_sync(0xffffffffu, P != 0.0f);
           if (any_p) {
-            live = a.W + 2;
+            live = W + 2;
             ring_dirty = true;
           }
           if (live > 0) {
@@ -418,25 +624,25 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep2_kernel(VjpArgs a) {
             }
             if (--live == 0) Y = 0.0;
           }
+          if (act) {
+            Cv = (float)((double)(Sv + P) * Sbar - Y);
+            xnext = x;
+            slot = slot == 0 ? ring_slots - 1 : slot - 1;
+          }
+          Cbuf[r * kVjpBand + tid] = Cv;
+          Pbuf[r * kVjpBand + tid] = pd;
         }
-        if (act) {
-          Cv = (float)((double)(Sv + P) * Sbar - Y);
-          xnext = x;
-          slot = slot == 0 ? a.ring_slots - 1 : slot - 1;
-        }
-        Cbuf[r * kVjpBand + tid] = Cv;
-        Pbuf[r * kVjpBand + tid] = pd;
       }
       __syncthreads();
       // ---- phase C: contract the block tiles
-      if (a.mask & 1) {  // dQz[i] += sum_j C(i, j) kz[j]
+      if (mask & 1) {  // dQz[i] += sum_j C(i, j) kz[j]
         for (int r = warp; r < nrows; r += kVjpWarps) {
-          float acc[DPAD];
+          float acc[DPAD < 8 ? 8 : DPAD];
 #pragma unroll
-          for (int d = 0; d < DPAD; ++d) acc[d] = 0.0f;
+          for (int d = 0; d < (DPAD < 8 ? 8 : DPAD); ++d) acc[d] = 0.0f;
 #pragma unroll
-          for (int c = 0; c < kVjpBand / 32; ++c) {
-            const int t = lane + 32 * c;
+          for (int cc = 0; cc < kVjpBand / 32; ++cc) {
+            const int t = lane + 32 * cc;
             const float cv = Cbuf[r * kVjpBand + t];
             const float4* kr =
                 reinterpret_cast<const float4*>(kz + (r + kVjpBand - 1 - t) * DPAD);
@@ -449,22 +655,25 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep2_kernel(VjpArgs a) {
               acc[4 * d4 + 3] += cv * kk.w;
             }
           }
-          float mine = 0.0f;
+          const int slot8 = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
 #pragma unroll
-          for (int d = 0; d < DPAD; ++d) {
-            const float s = warp_sum(acc[d]);
-            if (lane == d) mine = s;
-          }
-          if (lane < a.D) {
-            float* dst = a.dq_part + (it.rowslot + i0 + r) * a.D + lane;
-            *dst = (w == it.w_begin) ? mine : *dst + mine;
+          for (int d0 = 0; d0 < (DPAD < 8 ? 8 : DPAD); d0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int d = 0; d < 8; ++d) v[d] = acc[d0 + d];
+            const float total = warp_reduce8(v, lane);
+            const int d = d0 + slot8;
+            if ((lane & 3) == 0 && d < D) {
+              float* dst = a.dq_part + (it.rowslot + i0 + r) * D + d;
+              *dst = (w == it.w_begin) ? total : *dst + total;
+            }
           }
         }
       }
-      if (a.mask & 6) {  // column sums: dKz[j] += sum_i C(i,j) qz[i];  dVz[j+1] += sum_i pd gO(i)
+      if (mask & 6) {  // column sums: dKz[j] += sum_i C(i,j) qz[i];  dVz[j+1] += sum_i pd gO(i)
         const int ncols = nrows + kVjpBand - 1;
-        for (int dv0 = 0; dv0 < ((a.mask & 4) ? a.Dv : 1); dv0 += DVPAD) {
-          if (a.mask & 4) {
+        for (int dv0 = 0; dv0 < ((mask & 4) ? a.Dv : 1); dv0 += DVPAD) {
+          if (mask & 4) {
             if (dv0 > 0) __syncthreads();
             for (int e = tid; e < nrows * DVPAD; e += kVjpBand) {
               const int r = e / DVPAD, d = e - r * DVPAD;
@@ -477,6 +686,7 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep2_kernel(VjpArgs a) {
             }
             __syncthreads();
           }
+          const bool do_k = (mask & 2) && dv0 == 0, do_v = (mask & 4) != 0;
           for (int c = tid; c < ncols; c += kVjpBand) {
             const int j = jwin0 + c;
             if (j < 0 || j > it.len - 1 - dmin) continue;
@@ -486,12 +696,16 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep2_kernel(VjpArgs a) {
 #pragma unroll
             for (int d = 0; d < DVPAD; ++d) accv[d] = 0.0f;
             // every thread walks the same rows so that a warp reads one tile row at a
-            // time (consecutive columns = consecutive diagonals, no bank conflicts)
+            // time (consecutive columns = consecutive diagonals, no bank conflicts);
+            // cells outside the band are masked to zero instead of branched around
+            const int tbase = kVjpBand - 1 - c;   // diagonal slot of (row 0, column j)
+#pragma unroll 4
             for (int r = 0; r < nrows; ++r) {
-              const int t = i0 + r - j - dmin;  // diagonal of cell (row, column j) in the band
-              if (t < 0 || t >= kVjpBand) continue;
-              if ((a.mask & 2) && dv0 == 0) {
-                const float cv = Cbuf[r * kVjpBand + t];
+              const int t = tbase + r;
+              const bool in = (unsigned)t < (unsigned)kVjpBand;
+              const int off = r * kVjpBand + (in ? t : 0);
+              if (do_k) {
+                const float cv = in ? Cbuf[off] : 0.0f;
                 const float4* qr = reinterpret_cast<const float4*>(qz + r * DPAD);
 #pragma unroll
                 for (int d4 = 0; d4 < DPAD / 4; ++d4) {
@@ -502,8 +716,8 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep2_kernel(VjpArgs a) {
                   acck[4 * d4 + 3] += cv * qq.w;
                 }
               }
-              if (a.mask & 4) {
-                const float pv = Pbuf[r * kVjpBand + t];
+              if (do_v) {
+                const float pv = in ? Pbuf[off] : 0.0f;
                 const float4* gr = reinterpret_cast<const float4*>(gob + r * DVPAD);
 #pragma unroll
                 for (int d4 = 0; d4 < DVPAD / 4; ++d4) {
@@ -518,13 +732,13 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep2_kernel(VjpArgs a) {
             // the first block (from the bottom) that touches column j writes, later ones add
             const int i_top = min(j + dmax, it.len - 1);
             const bool first = (w == it.w_begin) && (rb == i_top / kVjpRows);
-            if ((a.mask & 2) && dv0 == 0) {
-              float* dst = a.dk_part + (it.rowslot + j) * a.D;
+            if (do_k) {
+              float* dst = a.dk_part + (it.rowslot + j) * D;
 #pragma unroll
               for (int d = 0; d < DPAD; ++d)
-                if (d < a.D) dst[d] = first ? acck[d] : dst[d] + acck[d];
+                if (d < D) dst[d] = first ? acck[d] : dst[d] + acck[d];
             }
-            if (a.mask & 4) {
+            if (do_v) {
               float* dst = a.dv_part + (it.rowslot + j + 1) * a.Dv + dv0;
 #pragma unroll
               for (int d = 0; d < DVPAD; ++d)
@@ -536,7 +750,7 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep2_kernel(VjpArgs a) {
     }
     // leave the ring zeroed for the next band of this item
     if (ring != nullptr && ring_dirty && w + 1 < it.w_end) {
-      for (int s = 0; s < a.ring_slots; ++s) ring[(int64_t)s * kVjpBand] = 0.0f;
+      for (int s = 0; s < ring_slots; ++s) ring[(int64_t)s * kVjpBand] = 0.0f;
     }
   }
 }
@@ -585,10 +799,11 @@ __global__ void vjp_finalize_kernel(VjpArgs a, int which) {
 
 template <int DPAD, int DVPAD>
 int launch_sweep2_t(const VjpArgs& a, int items_upper, bool small_dv, cudaStream_t stream) {
-  const size_t floats = kSweepCommonFloats + 2 * kVjpRows * kVjpBand +
-                        (size_t)(kVjpRows + kVjpBand) * DPAD + kVjpRows * DPAD + kVjpRows * DVPAD;
+  const int ngroups = small_dv ? (a.Dv + 3) / 4 : 0;
+  const size_t floats = sweep_common_floats(ngroups) + 2 * kVjpRows * kVjpBand +
+                        (size_t)kWinCols * DPAD + kVjpRows * DPAD + kVjpRows * DVPAD;
   const size_t bytes = floats * sizeof(float);
-  dim3 grid((unsigned)items_upper, (unsigned)a.H);
+  const unsigned grid = (unsigned)((int64_t)items_upper * a.H);
   if (small_dv) {
     ROSA_CUDA_OK(cudaFuncSetAttribute(vjp_sweep2_kernel<DPAD, DVPAD, true>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
@@ -634,12 +849,21 @@ int launch_pack_value_bits(const void* v, int dtype, int64_t N, int Hv, int Dv, 
 int launch_vjp_sweep1(const VjpArgs& a, int items_upper, cudaStream_t stream) {
   if (items_upper <= 0) return 0;
   ProfileScope prof("vjp_sweep1", stream);
-  const size_t bytes = kSweepCommonFloats * sizeof(float);
-  dim3 grid((unsigned)items_upper, (unsigned)a.H);
-  if (a.Dv <= 32)
-    vjp_sweep1_kernel<true><<<grid, kVjpBand, bytes, stream>>>(a);
+  const bool small_dv = a.Dv <= 32;
+  const size_t bytes = sweep_common_floats(small_dv ? (a.Dv + 3) / 4 : 0) * sizeof(float);
+  const unsigned grid = (unsigned)((int64_t)items_upper * a.H);
+  // the analytic logit bound is a safe softmax reference while it stays far inside the
+  // float exponent range; otherwise every row reduces its own maximum
+  const float top = a.scale * kSqrtScale * (sqrtf(1.0f + (float)a.W) - 1.0f);
+  const bool fixed_ref = top <= 80.0f;
+  if (small_dv && fixed_ref)
+    vjp_sweep1_kernel<true, true><<<grid, kVjpBand, bytes, stream>>>(a);
+  else if (small_dv)
+    vjp_sweep1_kernel<true, false><<<grid, kVjpBand, bytes, stream>>>(a);
+  else if (fixed_ref)
+    vjp_sweep1_kernel<false, true><<<grid, kVjpBand, bytes, stream>>>(a);
   else
-    vjp_sweep1_kernel<false><<<grid, kVjpBand, bytes, stream>>>(a);
+    vjp_sweep1_kernel<false, false><<<grid, kVjpBand, bytes, stream>>>(a);
   ROSA_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -96,6 +96,8 @@ SHAPES = [
     (1, 20, 1, 4, 1, 3000, 4, 1.0, 0.0, 3.0, torch.float32),     # very wide value rows
     (3, 1, 2, 3, 1, 2, 4, 1.0, 0.0, 3.0, torch.float32),         # singleton sequences
     (2, 2, 1, 1, 1, 1, 1, 1.0, 0.0, 3.0, torch.float32),
+    (1, 290, 2, 4, 1, 8, 200, 9.0, 0.1, 3.0, torch.float32),     # large scale: per-row softmax max
+    (1, 150, 2, 6, 1, 36, 60, 12.0, 0.0, 2.0, torch.float32),    # same with wide value rows
 ]
 
 
