@@ -336,13 +336,14 @@ static void vjp_one(const uint32_t* qs, const uint32_t* ks, /* [len] symbols of 
  * q,k [N,H,D]; v [N,Hv,Dv]; go [N,H,Dv] (all float32 values of the input dtype);
  * outputs double [N,H,D], [N,H,D], [N,Hv,Dv]; pass NULL to skip one.
  * Dropout "batch" coordinate = sequence ordinal counting empty sequences
- * (rosa_soft/soft_reference.py:683-699) plus batch_offset.  has_seed = 0 means p == 0. */
+ * (rosa_soft/soft_reference.py:683-699) plus batch_offset; head_offset shifts the head
+ * coordinate the same way (both are zero for an unsharded problem). */
 ORACLE_API void oracle_surrogate_vjp(const float* q, const float* k, const float* v,
                                      const float* go, const int64_t* cu_seqlens, int64_t num_seq,
                                      int64_t N, int H, int D, int Hv, int Dv, int64_t W,
                                      double scale, double dropout_p, double mismatch_scale,
-                                     int64_t seed, int64_t batch_offset, double* dq, double* dk,
-                                     double* dv) {
+                                     int64_t seed, int64_t batch_offset, int64_t head_offset,
+                                     double* dq, double* dk, double* dv) {
   const int group = H / Hv;
   uint32_t* qs = (uint32_t*)malloc(sizeof(uint32_t) * (size_t)(N * H));
   uint32_t* ks = (uint32_t*)malloc(sizeof(uint32_t) * (size_t)(N * H));
@@ -375,7 +376,8 @@ ORACLE_API void oracle_surrogate_vjp(const float* q, const float* k, const float
         if (dKz) memset(dKz, 0, sizeof(double) * (size_t)(len * D));
         vjp_one(ql, kl, v + (start * Hv + vh) * Dv, (int64_t)Hv * Dv,
                 go + (start * H + h) * Dv, (int64_t)H * Dv, len, D, Dv, Weff, scale, dropout_p,
-                mismatch_scale, (uint64_t)seed, (uint32_t)h, (uint32_t)(s + batch_offset), dQz,
+                mismatch_scale, (uint64_t)seed, (uint32_t)(h + head_offset),
+                (uint32_t)(s + batch_offset), dQz,
                 dKz, dVz);
         for (int64_t t = 0; t < len; ++t)
           for (int d = 0; d < D; ++d) {

@@ -146,7 +146,7 @@ def hard_inference(qsym, ksym, payload, cu_seqlens, max_suffix_length):
 
 
 def surrogate_vjp(q, k, v, grad_out, cu_seqlens, max_suffix_length, scale=1.0, dropout_p=0.0,
-                  mismatch_scale=3.0, seed=0, batch_offset=0, mask=7):
+                  mismatch_scale=3.0, seed=0, batch_offset=0, mask=7, head_offset=0):
     """Float64 gradients (dq, dk, dv) of the reference's dense surrogate; None where masked off."""
     q, k, v, go = _f32(q), _f32(k), _f32(v), _f32(grad_out)
     n, h, d = q.shape
@@ -160,7 +160,7 @@ def surrogate_vjp(q, k, v, grad_out, cu_seqlens, max_suffix_length, scale=1.0, d
         _p(cu, ctypes.c_int64), ctypes.c_int64(len(cu) - 1), ctypes.c_int64(n), ctypes.c_int(h),
         ctypes.c_int(d), ctypes.c_int(hv), ctypes.c_int(dv), ctypes.c_int64(max_suffix_length),
         ctypes.c_double(scale), ctypes.c_double(dropout_p), ctypes.c_double(mismatch_scale),
-        ctypes.c_int64(seed), ctypes.c_int64(batch_offset),
+        ctypes.c_int64(seed), ctypes.c_int64(batch_offset), ctypes.c_int64(head_offset),
         _p(dq, ctypes.c_double), _p(dk, ctypes.c_double), _p(dvv, ctypes.c_double),
     )
     return dq, dk, dvv
