@@ -69,6 +69,25 @@ ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, con
                            int32_t* route_token /* nullable, [N, H] */, void* workspace,
                            size_t workspace_bytes, void* stream);
 
+/* Hard forward without a workspace argument (no counterpart in the reference, whose
+ * operators always allocate through the framework).  For hosts that cannot allocate device
+ * memory at call time -- a server that gave all of it to its own arena and keeps the CUDA
+ * allocator out of its request loop, or an embedding host without a device-memory manager.
+ * Same inputs, outputs and results as rosa_b200_hard_forward; the scratch lives in a fixed
+ * array inside the library's device image (8 MiB + 128 KiB held by every GPU that loads the
+ * library, until the process exits).  Limits: N * H <= 1,048,576 token-heads and
+ * num_seq <= 4096; larger problems are rejected with an error and nothing is enqueued.
+ * The entry point calls no allocation routine.  The first call on a device resolves the
+ * array's device address (cudaGetSymbolAddress, with that device current); make that first
+ * call before starting any stream capture.  All calls on one GPU share the array, which
+ * keeps the previous call's contents: the parts that must start at zero are cleared on
+ * `stream` by each call, and calls that overlap on the same GPU race -- order them. */
+ROSA_B200_API int rosa_b200_hard_forward_static(
+    const void* query, const void* key, const void* value, int dtype, int64_t N, int H, int D,
+    int Hv, int Dv, const int32_t* cu_seqlens, int64_t num_seq, int64_t uniform_len,
+    int64_t max_suffix_length, void* output, int32_t* packed_query, int32_t* packed_key,
+    int32_t* route_token /* nullable, [N, H] */, void* stream);
+
 /* ------------------------------------------------------------- surrogate VJP
  * Replaces surrogate_vjp_cuda / surrogate_vjp_varlen_cuda
  * (reference rosa_soft/csrc/rosa_soft.cpp:26-55, kernels

@@ -19,6 +19,7 @@ EXPORTED_SYMBOLS = (
     "rosa_b200_last_error",
     "rosa_b200_hard_forward_workspace_bytes",
     "rosa_b200_hard_forward",
+    "rosa_b200_hard_forward_static",
     "rosa_b200_surrogate_vjp_workspace_bytes",
     "rosa_b200_surrogate_vjp",
     "rosa_b200_hard_inference_workspace_bytes",
@@ -47,6 +48,9 @@ def load() -> ctypes.CDLL:
     lib.rosa_b200_hard_forward.restype = i32
     lib.rosa_b200_hard_forward.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, i32, vp, i64, i64,
                                            i64, vp, vp, vp, vp, vp, sz, vp]
+    lib.rosa_b200_hard_forward_static.restype = i32
+    lib.rosa_b200_hard_forward_static.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, i32, vp, i64,
+                                                  i64, i64, vp, vp, vp, vp, vp]
     lib.rosa_b200_surrogate_vjp_workspace_bytes.restype = sz
     lib.rosa_b200_surrogate_vjp_workspace_bytes.argtypes = [i64, i32, i32, i32, i32, i64, i64, i64,
                                                             i32]
@@ -129,6 +133,33 @@ def hard_forward(q, k, v, cu_seqlens, max_suffix_length, want_routes=True, strea
                                      _ptr(pq), _ptr(pk), _ptr(routes), _ptr(ws), nbytes,
                                      ctypes.c_void_p(st)))
     return out, pq, pk, routes, ws
+
+
+def hard_forward_static(q, k, v, cu_seqlens, max_suffix_length, stream=None):
+    """Same as :func:`hard_forward` through the entry point that takes no workspace: the only
+    device memory touched besides the arguments is the fixed scratch array inside the library.
+    The output tensors below are the caller's buffers; the library allocates nothing."""
+    import torch
+
+    lib = load()
+    N, H, D = q.shape
+    Hv, Dv = v.shape[1:]
+    if isinstance(cu_seqlens, tuple):
+        S, T = cu_seqlens
+        cu, sym_shape = None, (S, H, T)
+    else:
+        S, T = cu_seqlens.numel() - 1, 0
+        cu, sym_shape = cu_seqlens, (H, N)
+    out = torch.empty((N, H, Dv), dtype=q.dtype, device=q.device)
+    pq = torch.empty(sym_shape, dtype=torch.int32, device=q.device)
+    pk = torch.empty_like(pq)
+    routes = torch.empty((N, H), dtype=torch.int32, device=q.device)
+    st = stream if stream is not None else torch.cuda.current_stream(q.device).cuda_stream
+    check(lib.rosa_b200_hard_forward_static(_ptr(q), _ptr(k), _ptr(v), dtype_code(q.dtype), N, H,
+                                            D, Hv, Dv, _ptr(cu), S, T, int(max_suffix_length),
+                                            _ptr(out), _ptr(pq), _ptr(pk), _ptr(routes),
+                                            ctypes.c_void_p(st)))
+    return out, pq, pk, routes
 
 
 def surrogate_vjp(q, k, v, go, cu_seqlens, packed_q, packed_k, max_suffix_length, scale=1.0,
