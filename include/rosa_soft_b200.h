@@ -41,6 +41,10 @@ extern "C" {
 
 enum rosa_b200_dtype { ROSA_B200_F32 = 0, ROSA_B200_F16 = 1, ROSA_B200_BF16 = 2 };
 
+/* Testing aid: OR-ed into gradient_mask, makes the backward contract its tiles on CUDA cores
+ * instead of the tensor core (both paths compute the same sums; tests compare them). */
+#define ROSA_B200_MASK_CUDA_CORE_CONTRACTION 0x100
+
 /* status word values reported by rosa_b200_read_status */
 enum rosa_b200_status {
   ROSA_B200_STATUS_OK = 0,

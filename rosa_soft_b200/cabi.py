@@ -178,7 +178,7 @@ def surrogate_vjp(q, k, v, go, cu_seqlens, packed_q, packed_k, max_suffix_length
         S, T = cu_seqlens.numel() - 1, 0
         cu = cu_seqlens
     f32 = dict(dtype=torch.float32, device=q.device)
-    dq = torch.empty((N, H, D), **f32) if mask & 1 else None
+    dq = torch.empty((N, H, D), **f32) if mask & 1 else None  # (mask bit 0x100: testing aid)
     dk = torch.empty((N, H, D), **f32) if mask & 2 else None
     dv = torch.empty((N, Hv, Dv), **f32) if mask & 4 else None
     nbytes = lib.rosa_b200_surrogate_vjp_workspace_bytes(N, H, D, Hv, Dv, S, T,

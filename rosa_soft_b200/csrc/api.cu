@@ -237,6 +237,7 @@ ROSA_B200_API size_t rosa_b200_surrogate_vjp_workspace_bytes(int64_t N, int H, i
                                                int64_t max_suffix_length, int gradient_mask) {
   const bool dense = uniform_len > 0;
   const int64_t W = std::min<int64_t>(max_suffix_length, dense ? uniform_len : N);
+  gradient_mask &= ~ROSA_B200_MASK_CUDA_CORE_CONTRACTION;
   return vjp_layout(N, H, D, Hv, Dv, num_seq, uniform_len, dense, W, gradient_mask).bytes;
 }
 
@@ -253,6 +254,8 @@ ROSA_B200_API int rosa_b200_surrogate_vjp(const void* query, const void* key, co
   if (int rc = check_problem(N, H, D, Hv, Dv, cu_seqlens, num_seq, uniform_len, max_suffix_length,
                              dtype))
     return rc;
+  const int force_cuda_cores = gradient_mask & ROSA_B200_MASK_CUDA_CORE_CONTRACTION;
+  gradient_mask &= ~ROSA_B200_MASK_CUDA_CORE_CONTRACTION;
   ROSA_REQUIRE(gradient_mask >= 1 && gradient_mask <= 7,
                "gradient_mask must be an integer bit mask in [1, 7]");
   ROSA_REQUIRE(query && key && value && grad_output && packed_query && packed_key && workspace,
@@ -295,6 +298,7 @@ ROSA_B200_API int rosa_b200_surrogate_vjp(const void* query, const void* key, co
   a.inv_keep = 1.0f / (1.0f - dropout_p);
   a.mismatch_scale = mismatch_scale;
   a.mask = gradient_mask;
+  a.force_cuda_core_contraction = force_cuda_cores != 0;
   a.batch_offset = (uint32_t)dropout_batch_offset;
   a.head_offset = (uint32_t)dropout_head_offset;
   a.ckpt = reinterpret_cast<int2*>(ws + l.ckpt_off);

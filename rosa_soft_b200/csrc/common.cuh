@@ -22,7 +22,7 @@ namespace rosa {
 
 // ------------------------------------------------------------------ constants
 constexpr int kVjpBand = 256;      // diagonals per surrogate-VJP band (= CTA threads)
-constexpr int kVjpRows = 32;       // rows per checkpointed block of the VJP sweeps
+constexpr int kVjpRows = 16;       // rows per checkpointed block of the VJP sweeps
 constexpr int kVjpWarps = kVjpBand / 32;
 constexpr int kFwdWarps = 4;       // warps per hard-forward CTA
 constexpr int kFwdPerLane = 8;     // diagonals per lane in the hard-forward matcher
@@ -288,6 +288,7 @@ struct VjpArgs {
   const int64_t* seed;
   float scale, dropout_p, inv_keep, mismatch_scale;
   int mask;
+  int force_cuda_core_contraction;  // debugging aid: contract on CUDA cores even when tcgen05 applies
   uint32_t batch_offset, head_offset;
   // scratch
   int2* ckpt;                      // (S bits, window mismatch sum) per (block, diagonal)

@@ -33,6 +33,7 @@
 #include <math_constants.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace rosa {
 
@@ -755,6 +756,347 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_kernel(VjpArgs a) {
   }
 }
 
+// ------------------------------------------------- sweep 2 on the tensor core
+// Same schedule as vjp_sweep2_kernel, but the three block contractions
+//     dKz[j] += sum_i C(i,j) qz[i]      dVz[j+1] += sum_i (p d)(i,j) gO(i)      dQz[i] += sum_j C(i,j) kz[j]
+// run as tcgen05.mma with fp32 accumulators in tensor memory.  The adjoint phase writes C
+// and p*d as bf16 (high, low) pairs -- 16 mantissa bits, the +-1 operands are exact -- into
+// un-skewed [row][window column] tiles made of 8x16-byte core matrices.  The same tile is
+// read MN-major (M = 128 window columns, K = the 16 block rows) for the column sums and
+// K-major (M = rows, K = window columns) for the row sums; the row-sum MMA uses M = 128 with
+// only the first 16 accumulator rows meaningful (the other rows read whatever follows the
+// tile in shared memory and are never looked at).  The 271-column window is covered by the
+// chunks [0,128), [128,256) and [144,272); only columns >= 256 of the last chunk are used.
+namespace tcl {
+constexpr int kColGroupBytes = 144;                       // 128-byte core + 16 bytes of skew
+constexpr int kRowGroupBytes = (kWinCols / 8) * kColGroupBytes;
+constexpr int kTileBytes = (kVjpRows / 8) * kRowGroupBytes;
+__host__ __device__ constexpr int chunk_start(int ch) { return ch == 0 ? 0 : ch == 1 ? 128 : kWinCols - 128; }
+static_assert(kVjpRows == 16, "one MMA k-step spans exactly the 16 rows of a block");
+__device__ __forceinline__ int tile_off(int r, int c) {
+  return (r >> 3) * kRowGroupBytes + (c >> 3) * kColGroupBytes + (r & 7) * 16 + (c & 7) * 2;
+}
+// B operand tiles, K-major: element (n, k) of an N x K matrix
+__device__ __forceinline__ int b_off(int n, int k, int N) {
+  return (k >> 3) * (N / 8 * 128) + (n >> 3) * 128 + (n & 7) * 16 + (k & 7) * 2;
+}
+__device__ __forceinline__ void store_split(unsigned char* hi, unsigned char* lo, int off,
+                                            float v) {
+  const __nv_bfloat16 h = __float2bfloat16_rn(v);
+  const __nv_bfloat16 l = __float2bfloat16_rn(v - __bfloat162float(h));
+  *reinterpret_cast<__nv_bfloat16*>(hi + off) = h;
+  *reinterpret_cast<__nv_bfloat16*>(lo + off) = l;
+}
+// bytes of the tensor-core operand area: 4 A tiles, qzT, gT hi/lo, kzT, mbarrier + tmem ptr
+__host__ __device__ inline int operand_bytes(int NK, int NV) {
+  return 4 * kTileBytes + NK * kVjpRows * 2 + 2 * NV * kVjpRows * 2 + NK * kWinCols * 2 + 16;
+}
+}  // namespace tcl
+
+template <int NK, int NV, bool kSmallDv>
+__global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
+  extern __shared__ float4 smem_raw[];
+  unsigned char* sbase = reinterpret_cast<unsigned char*>(smem_raw);
+  unsigned char* tChi = sbase;
+  unsigned char* tClo = tChi + tcl::kTileBytes;
+  unsigned char* tPhi = tClo + tcl::kTileBytes;
+  unsigned char* tPlo = tPhi + tcl::kTileBytes;
+  unsigned char* bQz = tPlo + tcl::kTileBytes;                 // [NK][kVjpRows]
+  unsigned char* bGhi = bQz + NK * kVjpRows * 2;               // [NV][kVjpRows]
+  unsigned char* bGlo = bGhi + NV * kVjpRows * 2;
+  unsigned char* bKz = bGlo + NV * kVjpRows * 2;               // [NK][kWinCols]
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(bKz + NK * kWinCols * 2);
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(mbar + 1);
+  const int ngroups = (a.Dv + 3) / 4;
+  SweepSmem sm = carve_common(reinterpret_cast<float*>(sbase + tcl::operand_bytes(NK, NV)), ngroups);
+  float* Sbuf = sm.rest;                               // [kVjpRows][kVjpBand] evidence S
+  float* Pbuf = Sbuf + kVjpRows * kVjpBand;            // [kVjpRows][kVjpBand] window product P
+
+  Item it;
+  if (!load_item_1d(a, &it)) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool dense = a.plan.cu_seqlens == nullptr;
+  const int64_t sym_base = (int64_t)it.seq * a.sym_seq_stride + (int64_t)it.h * a.sym_head_stride +
+                           (dense ? 0 : it.start);
+  const int32_t* __restrict__ q = a.qsym + sym_base;
+  const int32_t* __restrict__ k = a.ksym + sym_base;
+  const int vh = it.h / a.group;
+  const uint32_t* __restrict__ vb = a.vbits + ((int64_t)vh * a.N + it.start) * a.vwords;
+  const int W = a.W, D = a.D, Dv = a.Dv, mask = a.mask, ring_slots = a.ring_slots;
+  const float scale = a.scale, inv_keep = a.inv_keep;
+  const float neg_md = -a.mismatch_scale / (float)a.D;
+  const bool windowed = W <= it.len - 2;
+  const bool use_dropout = a.dropout_p > 0.0f;
+  const bool has_glo = a.dtype != ROSA_B200_BF16;   // bf16 grad_output is exact in one term
+  const float4* __restrict__ rowstat = a.rowstat + (int64_t)it.h * a.N + it.start;
+  float* ring = ring_slots ? a.ring + it.item_linear * (int64_t)ring_slots * kVjpBand + tid
+                           : nullptr;
+  constexpr uint32_t kTmemCols = (4 * NK + 3 * NV) <= 128 ? 128 : 256;
+  constexpr uint32_t kColK = 0, kColV = 3 * NK, kColQ = 3 * NK + 3 * NV;
+
+  // ---- one-time set-up: zero the A tiles (cells outside the band stay zero for ever),
+  // allocate tensor memory, initialise the mbarrier
+  for (int e = tid; e < 4 * tcl::kTileBytes / 16; e += kVjpBand)
+    reinterpret_cast<uint4*>(tChi)[e] = make_uint4(0, 0, 0, 0);
+  if (tid <= D) sm.glut[tid] = expf(neg_md * (float)tid);
+  if (warp == 0) tc::tmem_alloc(tmem_ptr, kTmemCols);
+  if (tid == 0) tc::mbar_init(mbar, 1);
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  tc::fence_after_thread_sync();
+  const uint32_t tmem = *tmem_ptr;
+  uint32_t mma_phase = 0;
+  bool mma_timed_out = false;
+
+  for (int w = it.w_begin; w < it.w_end; ++w) {
+    const int dmin = 1 + w * kVjpBand;
+    const int dmax = dmin + kVjpBand - 1;
+    const int delta = dmin + tid;
+    const bool valid = delta <= it.len - 1;
+    const int rb_lo = dmin / kVjpRows, rb_hi = (it.len - 1) / kVjpRows;
+    const int64_t ck_band = it.ck_base + vjp_ck_before(it.len, w);
+    double Sbar = 0.0, Y = 0.0;
+    float xnext = 0.0f;
+    int live = 0;
+    bool ring_dirty = false;
+    int slot = (valid && ring_slots) ? (it.len - 1 - delta) % ring_slots : 0;
+
+    for (int rb = rb_hi; rb >= rb_lo; --rb) {
+      const int i0 = max(rb * kVjpRows, dmin), i1 = min(rb * kVjpRows + kVjpRows - 1, it.len - 1);
+      const int nrows = i1 - i0 + 1;
+      const int jwin0 = i0 - dmax;  // first key column of the block's column window
+      const int64_t ck_idx = ck_band + (rb - rb_lo);
+      __syncthreads();
+      // ---- block tables
+      fill_block_windows<kSmallDv>(sm, it, q, k, vb, i0, nrows, jwin0, windowed, W, false);
+      if (tid < nrows) sm.rstat[tid] = rowstat[i0 + tid];
+      if (use_dropout && tid < nrows * kVjpWarps)
+        sm.s_keep[tid] = a.keepbits[(ck_idx * kVjpRows) * kVjpWarps + tid];
+      build_ulut(a, it, i0, nrows, ngroups, sm.ulut);
+      const int2 ck = a.ckpt[ck_idx * kVjpBand + tid];
+      __syncthreads();
+      // B operands of the block: qz^T [NK][rows], gO^T hi/lo [NV][rows], kz^T [NK][window cols]
+      if (mask & 2)
+        for (int e = tid; e < NK * kVjpRows; e += kVjpBand) {
+          const int d = e / kVjpRows, r = e - d * kVjpRows;
+          const float v = (d < D && r < nrows) ? ((sm.s_q[r] >> d & 1) ? 1.0f : -1.0f) : 0.0f;
+          *reinterpret_cast<__nv_bfloat16*>(bQz + tcl::b_off(d, r, NK)) = __float2bfloat16_rn(v);
+        }
+      if (mask & 4)
+        for (int e = tid; e < NV * kVjpRows; e += kVjpBand) {
+          const int d = e / kVjpRows, r = e - d * kVjpRows;
+          const float g = (d < Dv && r < nrows)
+                              ? load_as_float(a.go, (((int64_t)it.start + i0 + r) * a.H + it.h) * Dv + d,
+                                              a.dtype)
+                              : 0.0f;
+          tcl::store_split(bGhi, bGlo, tcl::b_off(d, r, NV), g);
+        }
+      if (mask & 1)
+        for (int e = tid; e < NK * kWinCols; e += kVjpBand) {
+          const int d = e / kWinCols, c = e - d * kWinCols;
+          const int j = jwin0 + c;
+          const float v = (d < D && c < nrows + kVjpBand - 1 && j >= 0 && j < it.len - 1)
+                              ? ((sm.s_k[c] >> d & 1) ? 1.0f : -1.0f)
+                              : 0.0f;
+          *reinterpret_cast<__nv_bfloat16*>(bKz + tcl::b_off(d, c, NK)) = __float2bfloat16_rn(v);
+        }
+      // ---- phase A: forward recurrence of the block from its checkpoint
+      float S = __int_as_float(ck.x);
+      int hs = ck.y;
+      const int r_first = valid ? max(0, delta - i0) : nrows;
+      const int cbase = kVjpBand - 1 - tid, jbase = i0 - delta;
+      bool has_p = false;
+#pragma unroll 4
+      for (int r = 0; r < nrows; ++r) {
+        const int c = cbase + r;
+        const float P = forward_cell(S, hs, r >= r_first, sm.s_q[r], sm.s_k[c], sm.s_qold[r],
+                                     sm.s_kold[c], jbase + r, sm.glut, windowed, W, neg_md);
+        has_p |= P != 0.0f;
+        Sbuf[r * kVjpBand + tid] = S;
+        Pbuf[r * kVjpBand + tid] = P;
+      }
+      // rows of a partial block that do not exist contribute nothing
+      for (int r = nrows; r < kVjpRows; ++r) {
+        const int off = tcl::tile_off(r, cbase + r);
+        tcl::store_split(tChi, tClo, off, 0.0f);
+        tcl::store_split(tPhi, tPlo, off, 0.0f);
+      }
+      // ---- phase B: adjoint recurrence, rows descending; C and p*d go to the operand tiles
+      const bool warp_p = ring != nullptr && __any_sync(0xffffffffu, has_p);
+      if (!warp_p && live == 0) {
+#pragma unroll 4
+        for (int r = nrows - 1; r >= 0; --r) {
+          const bool act = r >= r_first;
+          const int c = cbase + r;
+          const float Sv = Sbuf[r * kVjpBand + tid];
+          const float x = sm.glut[__popc(sm.s_q[r] ^ sm.s_k[c])];
+          float pd;
+          const float dS = cell_adjoint_seed<kSmallDv>(a, it, sm, vb, act, i0 + r, jbase + r, r, c,
+                                                       lane, warp, ngroups, use_dropout, scale,
+                                                       inv_keep, Sv, &pd);
+          Sbar = (double)dS + (double)xnext * Sbar;
+          const float Cv = act ? (float)((double)Sv * Sbar) : 0.0f;
+          const int off = tcl::tile_off(r, c);
+          tcl::store_split(tChi, tClo, off, Cv);
+          tcl::store_split(tPhi, tPlo, off, pd);
+          xnext = x;
+        }
+        if (valid && ring_slots) {
+          slot -= (nrows - r_first) % ring_slots;
+          if (slot < 0) slot += ring_slots;
+        }
+      } else {
+        for (int r = nrows - 1; r >= 0; --r) {
+          const bool act = r >= r_first;
+          const int c = cbase + r;
+          const float Sv = Sbuf[r * kVjpBand + tid];
+          const float P = Pbuf[r * kVjpBand + tid];
+          const float x = sm.glut[__popc(sm.s_q[r] ^ sm.s_k[c])];
+          float pd;
+          const float dS = cell_adjoint_seed<kSmallDv>(a, it, sm, vb, act, i0 + r, jbase + r, r, c,
+                                                       lane, warp, ngroups, use_dropout, scale,
+                                                       inv_keep, Sv, &pd);
+          float Cv = 0.0f;
+          double T = 0.0;
+          if (act) {
+            Sbar = (double)dS + (double)xnext * Sbar;
+            T = Sbar * (double)P;
+          }
+          const bool any_p = __any_sync(0xffffffffu, P != 0.0f);
+          if (any_p) {
+            live = W + 2;
+            ring_dirty = true;
+          }
+          if (live > 0) {
+            if (act) {
+              const float tf = (float)T;
+              const float old = ring[(int64_t)slot * kVjpBand];
+              ring[(int64_t)slot * kVjpBand] = tf;
+              Y += (double)tf - (double)old;
+            }
+            if (--live == 0) Y = 0.0;
+          }
+          if (act) {
+            Cv = (float)((double)(Sv + P) * Sbar - Y);
+            xnext = x;
+            slot = slot == 0 ? ring_slots - 1 : slot - 1;
+          }
+          const int off = tcl::tile_off(r, c);
+          tcl::store_split(tChi, tClo, off, Cv);
+          tcl::store_split(tPhi, tPlo, off, pd);
+        }
+      }
+      // ---- phase C: contract the block tiles on the tensor core
+      tc::fence_proxy_async_smem();
+      tc::fence_before_thread_sync();
+      __syncthreads();
+      if (tid == 0) {
+        tc::fence_after_thread_sync();
+        const uint32_t aChi = tc::smem_addr(tChi), aClo = tc::smem_addr(tClo);
+        const uint32_t aPhi = tc::smem_addr(tPhi), aPlo = tc::smem_addr(tPlo);
+        constexpr uint32_t idK = tc::idesc_bf16_f32(128, NK, true, false);
+        constexpr uint32_t idV = tc::idesc_bf16_f32(128, NV, true, false);
+        constexpr uint32_t idQ = tc::idesc_bf16_f32(128, NK, false, false);
+        const uint64_t dQz = tc::smem_desc(tc::smem_addr(bQz), NK / 8 * 128, 128);
+        const uint64_t dGhi = tc::smem_desc(tc::smem_addr(bGhi), NV / 8 * 128, 128);
+        const uint64_t dGlo = tc::smem_desc(tc::smem_addr(bGlo), NV / 8 * 128, 128);
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) {
+          const uint32_t shift = (tcl::chunk_start(ch) >> 3) * tcl::kColGroupBytes;
+          // MN-major view: K direction = row groups, M direction = column groups
+          if (mask & 2) {
+            tc::mma_bf16(tmem + kColK + ch * NK,
+                         tc::smem_desc(aChi + shift, tcl::kRowGroupBytes, tcl::kColGroupBytes), dQz,
+                         idK, false);
+            tc::mma_bf16(tmem + kColK + ch * NK,
+                         tc::smem_desc(aClo + shift, tcl::kRowGroupBytes, tcl::kColGroupBytes), dQz,
+                         idK, true);
+          }
+          if (mask & 4) {
+            const uint64_t dPhi =
+                tc::smem_desc(aPhi + shift, tcl::kRowGroupBytes, tcl::kColGroupBytes);
+            tc::mma_bf16(tmem + kColV + ch * NV, dPhi, dGhi, idV, false);
+            tc::mma_bf16(tmem + kColV + ch * NV,
+                         tc::smem_desc(aPlo + shift, tcl::kRowGroupBytes, tcl::kColGroupBytes), dGhi,
+                         idV, true);
+            if (has_glo) tc::mma_bf16(tmem + kColV + ch * NV, dPhi, dGlo, idV, true);
+          }
+        }
+        if (mask & 1) {
+          // K-major view: K direction = column groups (two per k-step), M direction = row groups
+          const uint32_t aKz = tc::smem_addr(bKz);
+          for (int ks = 0; ks < kWinCols / 16; ++ks) {
+            const uint64_t dKz = tc::smem_desc(aKz + ks * 2 * (NK / 8 * 128), NK / 8 * 128, 128);
+            const uint32_t shift = ks * 2 * tcl::kColGroupBytes;
+            tc::mma_bf16(tmem + kColQ,
+                         tc::smem_desc(aChi + shift, tcl::kColGroupBytes, tcl::kRowGroupBytes), dKz,
+                         idQ, ks > 0);
+            tc::mma_bf16(tmem + kColQ,
+                         tc::smem_desc(aClo + shift, tcl::kColGroupBytes, tcl::kRowGroupBytes), dKz,
+                         idQ, true);
+          }
+        }
+        tc::mma_commit(mbar);
+      }
+      // bounded wait: a lost completion sets a flag instead of hanging the GPU
+      if (!tc::mbar_wait(mbar, mma_phase, 1u << 24)) mma_timed_out = true;
+      mma_phase ^= 1u;
+      tc::fence_after_thread_sync();
+      // ---- epilogue: accumulators -> per-item partial gradients (this CTA owns them)
+      {
+        const int quarter = warp & 3;
+        const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
+        const bool k_half = warp < 4;
+        if (k_half ? (mask & 2) != 0 : (mask & 4) != 0) {
+#pragma unroll
+          for (int ch = 0; ch < 3; ++ch) {
+            const int c = tcl::chunk_start(ch) + 32 * quarter + lane;
+            const int j = jwin0 + c;
+            const bool use = (ch < 2 || c >= 256) && c < nrows + kVjpBand - 1 && j >= 0 &&
+                             j <= it.len - 1 - dmin;
+            const int i_top = min(j + dmax, it.len - 1);
+            const bool first = (w == it.w_begin) && (rb == i_top / kVjpRows);
+            constexpr int N = NK > NV ? NK : NV;
+            const int n = k_half ? NK : NV;
+            const int dim = k_half ? D : Dv;
+            for (int n0 = 0; n0 < n && n0 < N; n0 += 16) {
+              float v[16];
+              tc::tmem_ld16(tmem + lane_base + (k_half ? kColK + ch * NK : kColV + ch * NV) + n0, v);
+              if (use) {
+                float* dst = k_half ? a.dk_part + (it.rowslot + j) * D + n0
+                                    : a.dv_part + (it.rowslot + j + 1) * Dv + n0;
+#pragma unroll
+                for (int d = 0; d < 16; ++d)
+                  if (n0 + d < dim) dst[d] = first ? v[d] : dst[d] + v[d];
+              }
+            }
+          }
+        }
+        if ((mask & 1) && warp == 4) {
+          for (int n0 = 0; n0 < NK; n0 += 16) {
+            float v[16];
+            tc::tmem_ld16(tmem + kColQ + n0, v);   // accumulator rows 0..31 = block rows
+            if (lane < nrows) {
+              float* dst = a.dq_part + (it.rowslot + i0 + lane) * D + n0;
+#pragma unroll
+              for (int d = 0; d < 16; ++d)
+                if (n0 + d < D) dst[d] = (w == it.w_begin) ? v[d] : dst[d] + v[d];
+            }
+          }
+        }
+      }
+      tc::fence_before_thread_sync();
+    }
+    // leave the ring zeroed for the next band of this item
+    if (ring != nullptr && ring_dirty && w + 1 < it.w_end) {
+      for (int s = 0; s < ring_slots; ++s) ring[(int64_t)s * kVjpBand] = 0.0f;
+    }
+  }
+  __syncthreads();
+  if (mma_timed_out && tid == 0) atomicExch(a.plan.status + 1, 1);
+  if (warp == 0) tc::tmem_dealloc(tmem, kTmemCols);
+}
+
 // ------------------------------------------------------------------ finalize
 // Sums the per-item partials in item order and applies the softsign Jacobian.
 // which: 0 = query, 1 = key, 2 = value.
@@ -813,6 +1155,23 @@ int launch_sweep2_t(const VjpArgs& a, int items_upper, bool small_dv, cudaStream
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     vjp_sweep2_kernel<DPAD, DVPAD, false><<<grid, kVjpBand, bytes, stream>>>(a);
   }
+  ROSA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+template <int NK, int NV>
+int launch_sweep2_tc(const VjpArgs& a, int items_upper, cudaStream_t stream) {
+  const int ngroups = (a.Dv + 3) / 4;
+  size_t bytes = tcl::operand_bytes(NK, NV) +
+                 (sweep_common_floats(ngroups) + 2 * kVjpRows * kVjpBand) * sizeof(float);
+  // the row-sum MMA reads 16 row groups from the first two tiles: keep that range inside
+  // the allocation
+  const size_t over_read = tcl::kTileBytes + 16 * (size_t)tcl::kRowGroupBytes + 256;
+  if (bytes < over_read) bytes = over_read;
+  const unsigned grid = (unsigned)((int64_t)items_upper * a.H);
+  ROSA_CUDA_OK(cudaFuncSetAttribute(vjp_sweep2_tc_kernel<NK, NV, true>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  vjp_sweep2_tc_kernel<NK, NV, true><<<grid, kVjpBand, bytes, stream>>>(a);
   ROSA_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -880,6 +1239,13 @@ int launch_vjp_rowstats(const VjpArgs& a, cudaStream_t stream) {
 int launch_vjp_sweep2(const VjpArgs& a, int items_upper, cudaStream_t stream) {
   if (items_upper <= 0) return 0;
   ProfileScope prof("vjp_sweep2", stream);
+  if (a.Dv <= 32 && !a.force_cuda_core_contraction) {
+    // tensor-core contraction (tcgen05): operand N is 16 or 32 for both symbol and value dims
+    if (a.D <= 16 && a.Dv <= 16) return launch_sweep2_tc<16, 16>(a, items_upper, stream);
+    if (a.D <= 16) return launch_sweep2_tc<16, 32>(a, items_upper, stream);
+    if (a.Dv <= 16) return launch_sweep2_tc<32, 16>(a, items_upper, stream);
+    return launch_sweep2_tc<32, 32>(a, items_upper, stream);
+  }
   if (a.D <= 4) return launch_sweep2_d<4>(a, items_upper, stream);
   if (a.D <= 8) return launch_sweep2_d<8>(a, items_upper, stream);
   if (a.D <= 16) return launch_sweep2_d<16>(a, items_upper, stream);

@@ -172,6 +172,22 @@ def test_gradient_masks(cabi, mask):
             assert a is None
 
 
+def test_tensor_core_and_cuda_core_contractions_agree(cabi):
+    """The tcgen05 contraction (bf16 high/low operand pairs, fp32 accumulation in tensor
+    memory) against the plain CUDA-core contraction of the same tiles."""
+    for dt, T, D, Dv, W, p in ((torch.float32, 700, 8, 8, 64, 0.1), (torch.bfloat16, 300, 16, 32, 40, 0.0),
+                               (torch.float16, 290, 20, 12, 9, 0.0)):
+        H, Hv = 2, 1
+        q = nonzero_randn((T, H, D), 141, dt).to(DEV)
+        k = nonzero_randn((T, H, D), 142, dt).to(DEV)
+        v = nonzero_randn((T, Hv, Dv), 143, dt).to(DEV)
+        go = nonzero_randn((T, H, Dv), 144, dt).to(DEV)
+        tc = _run_cabi(cabi, q, k, v, go, (1, T), W, 1.0, p, 3.0, 5)[4:]
+        cc = _run_cabi(cabi, q, k, v, go, (1, T), W, 1.0, p, 3.0, 5, mask=7 | 0x100)[4:]
+        for x, y in zip(tc, cc):
+            assert normalised_error(x.cpu().numpy(), y.cpu().numpy()) <= 2e-5
+
+
 def test_backward_is_bitwise_reproducible(cabi):
     T, H, D, Hv, Dv, W = 1500, 4, 3, 2, 8, 33
     q = repeated_stream_logits(T, H, D, seed=8).to(DEV)
