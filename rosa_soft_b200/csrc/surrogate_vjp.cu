@@ -224,15 +224,15 @@ __device__ __forceinline__ void fill_block_windows(const SweepSmem& sm, const It
                                                    const int32_t* __restrict__ q,
                                                    const int32_t* __restrict__ k,
                                                    const uint32_t* __restrict__ vb, int i0,
-                                                   int nrows, int jwin0, bool windowed, int W,
-                                                   bool want_hash) {
+                                                   int nrows, int jwin0, int ncols, bool windowed,
+                                                   int W, bool want_hash) {
   const int tid = threadIdx.x;
   if (tid < nrows) {
     const int i = i0 + tid;
     sm.s_q[tid] = __ldg(q + i);
     sm.s_qold[tid] = (windowed && i - W - 1 >= 0) ? __ldg(q + i - W - 1) : 0;
   }
-  for (int c = tid; c < nrows + kVjpBand - 1; c += kVjpBand) {
+  for (int c = tid; c < ncols; c += kVjpBand) {
     const int j = jwin0 + c;
     const bool in = j >= 0 && j < it.len - 1;  // a key column of some cell
     sm.s_k[c] = in ? __ldg(k + j) : 0;
@@ -341,7 +341,8 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
       const int jwin0 = i0 - dmax;
       const int64_t ck_idx = ck_band + (rb - rb_lo);
       __syncthreads();
-      fill_block_windows<kSmallDv>(sm, it, q, k, vb, i0, nrows, jwin0, windowed, W, use_dropout);
+      fill_block_windows<kSmallDv>(sm, it, q, k, vb, i0, nrows, jwin0, nrows + kVjpBand - 1, windowed, W,
+                                   use_dropout);
       if (tid < nrows) sm.rstat[tid].w = logf((float)(i0 + tid));
       if (kSmallDv) build_ulut(a, it, i0, nrows, ngroups, sm.ulut);
       __syncthreads();
@@ -537,7 +538,8 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_kernel(VjpArgs a) {
       const int64_t ck_idx = ck_band + (rb - rb_lo);
       __syncthreads();
       // ---- block tables
-      fill_block_windows<kSmallDv>(sm, it, q, k, vb, i0, nrows, jwin0, windowed, W, false);
+      fill_block_windows<kSmallDv>(sm, it, q, k, vb, i0, nrows, jwin0, nrows + kVjpBand - 1, windowed, W,
+                                   false);
       if (tid < nrows) sm.rstat[tid] = rowstat[i0 + tid];
       if (use_dropout && tid < nrows * kVjpWarps)
         sm.s_keep[tid] = a.keepbits[(ck_idx * kVjpRows) * kVjpWarps + tid];
@@ -793,22 +795,45 @@ __host__ __device__ inline int operand_bytes(int NK, int NV) {
 }
 }  // namespace tcl
 
-template <int NK, int NV, bool kSmallDv>
+// geometry of one row block, kept in registers for the deferred epilogue
+struct TcBlock {
+  int w, rb, i0, nrows, jwin, dmin, dmax;
+  bool pending;
+};
+
+// Shared-memory plan of the tensor-core kernel (bytes from the start of dynamic smem).
+template <int NK, int NV>
+struct TcSmem {
+  static constexpr int kKzSlots = kWinCols / 16 + 2;            // circular k-steps of kz^T
+  static constexpr int kKzSlotBytes = NK * 32;                  // [NK][16] bf16
+  static constexpr int kQzBytes = NK * kVjpRows * 2;
+  static constexpr int kGBytes = NV * kVjpRows * 2;
+  static constexpr int oQz = 4 * tcl::kTileBytes;               // two buffers
+  static constexpr int oGhi = oQz + 2 * kQzBytes;               // two buffers
+  static constexpr int oGlo = oGhi + 2 * kGBytes;               // two buffers
+  static constexpr int oKz = oGlo + 2 * kGBytes;
+  static constexpr int oBar = oKz + kKzSlots * kKzSlotBytes;
+  static constexpr int kBytes = oBar + 16;
+};
+
+// Software pipeline per CTA: the MMAs of block b run on the tensor core while the CUDA
+// cores fill the tables and run the forward recurrence of block b+1; the accumulators of
+// block b are read back just before the adjoint phase of block b+1 overwrites the operand
+// tiles.  B operands are double buffered, kz^T is a ring of k-steps keyed by the absolute
+// key-column group (consecutive blocks share all but one group).
+template <int NK, int NV, int NG, bool kWindowed, bool kDropout>
 __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
+  using L = TcSmem<NK, NV>;
   extern __shared__ float4 smem_raw[];
   unsigned char* sbase = reinterpret_cast<unsigned char*>(smem_raw);
   unsigned char* tChi = sbase;
   unsigned char* tClo = tChi + tcl::kTileBytes;
   unsigned char* tPhi = tClo + tcl::kTileBytes;
   unsigned char* tPlo = tPhi + tcl::kTileBytes;
-  unsigned char* bQz = tPlo + tcl::kTileBytes;                 // [NK][kVjpRows]
-  unsigned char* bGhi = bQz + NK * kVjpRows * 2;               // [NV][kVjpRows]
-  unsigned char* bGlo = bGhi + NV * kVjpRows * 2;
-  unsigned char* bKz = bGlo + NV * kVjpRows * 2;               // [NK][kWinCols]
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(bKz + NK * kWinCols * 2);
+  unsigned char* bKz = sbase + L::oKz;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(sbase + L::oBar);
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(mbar + 1);
-  const int ngroups = (a.Dv + 3) / 4;
-  SweepSmem sm = carve_common(reinterpret_cast<float*>(sbase + tcl::operand_bytes(NK, NV)), ngroups);
+  SweepSmem sm = carve_common(reinterpret_cast<float*>(sbase + L::kBytes), NG);
   float* Sbuf = sm.rest;                               // [kVjpRows][kVjpBand] evidence S
   float* Pbuf = Sbuf + kVjpRows * kVjpBand;            // [kVjpRows][kVjpBand] window product P
 
@@ -825,8 +850,6 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   const int W = a.W, D = a.D, Dv = a.Dv, mask = a.mask, ring_slots = a.ring_slots;
   const float scale = a.scale, inv_keep = a.inv_keep;
   const float neg_md = -a.mismatch_scale / (float)a.D;
-  const bool windowed = W <= it.len - 2;
-  const bool use_dropout = a.dropout_p > 0.0f;
   const bool has_glo = a.dtype != ROSA_B200_BF16;   // bf16 grad_output is exact in one term
   const float4* __restrict__ rowstat = a.rowstat + (int64_t)it.h * a.N + it.start;
   float* ring = ring_slots ? a.ring + it.item_linear * (int64_t)ring_slots * kVjpBand + tid
@@ -834,8 +857,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   constexpr uint32_t kTmemCols = (4 * NK + 3 * NV) <= 128 ? 128 : 256;
   constexpr uint32_t kColK = 0, kColV = 3 * NK, kColQ = 3 * NK + 3 * NV;
 
-  // ---- one-time set-up: zero the A tiles (cells outside the band stay zero for ever),
-  // allocate tensor memory, initialise the mbarrier
+  // ---- one-time set-up
   for (int e = tid; e < 4 * tcl::kTileBytes / 16; e += kVjpBand)
     reinterpret_cast<uint4*>(tChi)[e] = make_uint4(0, 0, 0, 0);
   if (tid <= D) sm.glut[tid] = expf(neg_md * (float)tid);
@@ -847,6 +869,59 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   const uint32_t tmem = *tmem_ptr;
   uint32_t mma_phase = 0;
   bool mma_timed_out = false;
+  int buf = 0;                       // B-operand buffer of the block being built
+  TcBlock prev;
+  prev.pending = false;
+
+  // Reads the accumulators of a finished block and adds them to the per-item partials.
+  auto epilogue = [&](const TcBlock& b) {
+    if (!tc::mbar_wait(mbar, mma_phase, 1u << 24)) mma_timed_out = true;
+    mma_phase ^= 1u;
+    tc::fence_after_thread_sync();
+    const int quarter = warp & 3;
+    const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
+    const bool k_half = warp < 4;
+    const int ncols = b.nrows + kVjpBand - 1 + (b.i0 - b.rb * kVjpRows);
+    if (k_half ? (mask & 2) != 0 : (mask & 4) != 0) {
+#pragma unroll
+      for (int ch = 0; ch < 3; ++ch) {
+        const int c = tcl::chunk_start(ch) + 32 * quarter + lane;
+        const int j = b.jwin + c;
+        const bool use =
+            (ch < 2 || c >= 256) && c < ncols && j >= 0 && j <= it.len - 1 - b.dmin;
+        const int i_top = min(j + b.dmax, it.len - 1);
+        const bool first = (b.w == it.w_begin) && (b.rb == i_top / kVjpRows);
+        constexpr int n = NK;   // placate unused warnings when NK == NV
+        (void)n;
+        const int ncol = k_half ? NK : NV;
+        const int dim = k_half ? D : Dv;
+        for (int n0 = 0; n0 < ncol; n0 += 16) {
+          float v[16];
+          tc::tmem_ld16(tmem + lane_base + (k_half ? kColK + ch * NK : kColV + ch * NV) + n0, v);
+          if (use) {
+            float* dst = k_half ? a.dk_part + (it.rowslot + j) * D + n0
+                                : a.dv_part + (it.rowslot + j + 1) * Dv + n0;
+#pragma unroll
+            for (int d = 0; d < 16; ++d)
+              if (n0 + d < dim) dst[d] = first ? v[d] : dst[d] + v[d];
+          }
+        }
+      }
+    }
+    if ((mask & 1) && warp == 4) {
+      for (int n0 = 0; n0 < NK; n0 += 16) {
+        float v[16];
+        tc::tmem_ld16(tmem + kColQ + n0, v);   // accumulator rows 0..31 = block rows
+        if (lane < b.nrows) {
+          float* dst = a.dq_part + (it.rowslot + b.i0 + lane) * D + n0;
+#pragma unroll
+          for (int d = 0; d < 16; ++d)
+            if (n0 + d < D) dst[d] = (b.w == it.w_begin) ? v[d] : dst[d] + v[d];
+        }
+      }
+    }
+    tc::fence_before_thread_sync();
+  };
 
   for (int w = it.w_begin; w < it.w_end; ++w) {
     const int dmin = 1 + w * kVjpBand;
@@ -864,18 +939,29 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     for (int rb = rb_hi; rb >= rb_lo; --rb) {
       const int i0 = max(rb * kVjpRows, dmin), i1 = min(rb * kVjpRows + kVjpRows - 1, it.len - 1);
       const int nrows = i1 - i0 + 1;
-      const int jwin0 = i0 - dmax;  // first key column of the block's column window
+      const int skew = i0 - rb * kVjpRows;       // 1 on the top block of a band, else 0
+      const int jwin = rb * kVjpRows - dmax;     // window start, a multiple of 16
+      const int ncols = nrows + kVjpBand - 1 + skew;
       const int64_t ck_idx = ck_band + (rb - rb_lo);
-      __syncthreads();
+      unsigned char* bQz = sbase + L::oQz + buf * L::kQzBytes;
+      unsigned char* bGhi = sbase + L::oGhi + buf * L::kGBytes;
+      unsigned char* bGlo = sbase + L::oGlo + buf * L::kGBytes;
+      // the bottom block of a band refills the whole kz^T ring: the last block of the
+      // previous band must have released it
+      if (rb == rb_hi && prev.pending) {
+        epilogue(prev);
+        prev.pending = false;
+      }
+      // (sync 2 of the previous block already separates its phase B from these writes)
       // ---- block tables
-      fill_block_windows<kSmallDv>(sm, it, q, k, vb, i0, nrows, jwin0, windowed, W, false);
+      fill_block_windows<true>(sm, it, q, k, vb, i0, nrows, jwin, ncols, kWindowed, W, false);
       if (tid < nrows) sm.rstat[tid] = rowstat[i0 + tid];
-      if (use_dropout && tid < nrows * kVjpWarps)
+      if (kDropout && tid < nrows * kVjpWarps)
         sm.s_keep[tid] = a.keepbits[(ck_idx * kVjpRows) * kVjpWarps + tid];
-      build_ulut(a, it, i0, nrows, ngroups, sm.ulut);
+      build_ulut(a, it, i0, nrows, NG, sm.ulut);
       const int2 ck = a.ckpt[ck_idx * kVjpBand + tid];
-      __syncthreads();
-      // B operands of the block: qz^T [NK][rows], gO^T hi/lo [NV][rows], kz^T [NK][window cols]
+      __syncthreads();                                                    // sync 1
+      // B operands of the block
       if (mask & 2)
         for (int e = tid; e < NK * kVjpRows; e += kVjpBand) {
           const int d = e / kVjpRows, r = e - d * kVjpRows;
@@ -891,30 +977,41 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
                               : 0.0f;
           tcl::store_split(bGhi, bGlo, tcl::b_off(d, r, NV), g);
         }
-      if (mask & 1)
-        for (int e = tid; e < NK * kWinCols; e += kVjpBand) {
-          const int d = e / kWinCols, c = e - d * kWinCols;
-          const int j = jwin0 + c;
-          const float v = (d < D && c < nrows + kVjpBand - 1 && j >= 0 && j < it.len - 1)
+      if (mask & 1) {
+        // kz^T ring: the bottom block of a band fills every k-step, later blocks only the
+        // one key-column group that entered the window
+        const int g0 = (jwin + (1 << 20)) >> 4;           // absolute group of window column 0
+        const int nfill = (rb == rb_hi) ? kWinCols / 16 : 1;
+        for (int e = tid; e < nfill * NK * 16; e += kVjpBand) {
+          const int ks = e / (NK * 16), rem = e - ks * (NK * 16);
+          const int d = rem >> 4, cc = rem & 15;
+          const int c = ks * 16 + cc;
+          const int j = jwin + c;
+          const float v = (d < D && j >= 0 && j < it.len - 1)
                               ? ((sm.s_k[c] >> d & 1) ? 1.0f : -1.0f)
                               : 0.0f;
-          *reinterpret_cast<__nv_bfloat16*>(bKz + tcl::b_off(d, c, NK)) = __float2bfloat16_rn(v);
+          const int sl = (g0 + ks) % L::kKzSlots;
+          *reinterpret_cast<__nv_bfloat16*>(bKz + sl * L::kKzSlotBytes + tcl::b_off(d, cc, NK)) =
+              __float2bfloat16_rn(v);
         }
+      }
       // ---- phase A: forward recurrence of the block from its checkpoint
       float S = __int_as_float(ck.x);
       int hs = ck.y;
       const int r_first = valid ? max(0, delta - i0) : nrows;
-      const int cbase = kVjpBand - 1 - tid, jbase = i0 - delta;
+      const int cbase = kVjpBand - 1 - tid + skew, jbase = i0 - delta;
       bool has_p = false;
 #pragma unroll 4
       for (int r = 0; r < nrows; ++r) {
         const int c = cbase + r;
         const float P = forward_cell(S, hs, r >= r_first, sm.s_q[r], sm.s_k[c], sm.s_qold[r],
-                                     sm.s_kold[c], jbase + r, sm.glut, windowed, W, neg_md);
+                                     sm.s_kold[c], jbase + r, sm.glut, kWindowed, W, neg_md);
         has_p |= P != 0.0f;
         Sbuf[r * kVjpBand + tid] = S;
-        Pbuf[r * kVjpBand + tid] = P;
+        if (kWindowed) Pbuf[r * kVjpBand + tid] = P;
       }
+      // ---- the previous block's MMAs have had the whole table/forward phase to finish
+      if (prev.pending) epilogue(prev);
       // rows of a partial block that do not exist contribute nothing
       for (int r = nrows; r < kVjpRows; ++r) {
         const int off = tcl::tile_off(r, cbase + r);
@@ -922,7 +1019,23 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
         tcl::store_split(tPhi, tPlo, off, 0.0f);
       }
       // ---- phase B: adjoint recurrence, rows descending; C and p*d go to the operand tiles
-      const bool warp_p = ring != nullptr && __any_sync(0xffffffffu, has_p);
+      const bool warp_p = kWindowed && ring != nullptr && __any_sync(0xffffffffu, has_p);
+      auto seed = [&](bool act, int r, int c, float Sv, float* pd) {
+        const float4 st = sm.rstat[r];
+        const float sq = sqrtf(1.0f + Sv);
+        const float logit = kSqrtScale * (sq - 1.0f) * scale - st.w;
+        const float pr = act ? __expf(logit - st.x) * st.y : 0.0f;
+        float dmul = 1.0f;
+        if (kDropout) dmul = (sm.s_keep[r * kVjpWarps + warp] >> lane & 1u) ? inv_keep : 0.0f;
+        const uint32_t bits = sm.s_vb[c];
+        const float* lut = sm.ulut + r * NG * 16;
+        float u = 0.0f;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) u += lut[g * 16 + ((bits >> (4 * g)) & 15u)];
+        *pd = pr * dmul;
+        const float dlogit = *pd * u - pr * st.z;
+        return scale * dlogit * (0.5f * kSqrtScale) * __frcp_rn(sq);
+      };
       if (!warp_p && live == 0) {
 #pragma unroll 4
         for (int r = nrows - 1; r >= 0; --r) {
@@ -931,9 +1044,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
           const float Sv = Sbuf[r * kVjpBand + tid];
           const float x = sm.glut[__popc(sm.s_q[r] ^ sm.s_k[c])];
           float pd;
-          const float dS = cell_adjoint_seed<kSmallDv>(a, it, sm, vb, act, i0 + r, jbase + r, r, c,
-                                                       lane, warp, ngroups, use_dropout, scale,
-                                                       inv_keep, Sv, &pd);
+          const float dS = seed(act, r, c, Sv, &pd);
           Sbar = (double)dS + (double)xnext * Sbar;
           const float Cv = act ? (float)((double)Sv * Sbar) : 0.0f;
           const int off = tcl::tile_off(r, c);
@@ -953,9 +1064,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
           const float P = Pbuf[r * kVjpBand + tid];
           const float x = sm.glut[__popc(sm.s_q[r] ^ sm.s_k[c])];
           float pd;
-          const float dS = cell_adjoint_seed<kSmallDv>(a, it, sm, vb, act, i0 + r, jbase + r, r, c,
-                                                       lane, warp, ngroups, use_dropout, scale,
-                                                       inv_keep, Sv, &pd);
+          const float dS = seed(act, r, c, Sv, &pd);
           float Cv = 0.0f;
           double T = 0.0;
           if (act) {
@@ -986,10 +1095,10 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
           tcl::store_split(tPhi, tPlo, off, pd);
         }
       }
-      // ---- phase C: contract the block tiles on the tensor core
+      // ---- phase C: hand the tiles to the tensor core
       tc::fence_proxy_async_smem();
       tc::fence_before_thread_sync();
-      __syncthreads();
+      __syncthreads();                                                    // sync 2
       if (tid == 0) {
         tc::fence_after_thread_sync();
         const uint32_t aChi = tc::smem_addr(tChi), aClo = tc::smem_addr(tClo);
@@ -1000,98 +1109,53 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
         const uint64_t dQz = tc::smem_desc(tc::smem_addr(bQz), NK / 8 * 128, 128);
         const uint64_t dGhi = tc::smem_desc(tc::smem_addr(bGhi), NV / 8 * 128, 128);
         const uint64_t dGlo = tc::smem_desc(tc::smem_addr(bGlo), NV / 8 * 128, 128);
+        // MN-major view (column sums): K direction = row groups, M direction = column groups
+        const uint64_t mnChi = tc::smem_desc(aChi, tcl::kRowGroupBytes, tcl::kColGroupBytes);
+        const uint64_t mnClo = tc::smem_desc(aClo, tcl::kRowGroupBytes, tcl::kColGroupBytes);
+        const uint64_t mnPhi = tc::smem_desc(aPhi, tcl::kRowGroupBytes, tcl::kColGroupBytes);
+        const uint64_t mnPlo = tc::smem_desc(aPlo, tcl::kRowGroupBytes, tcl::kColGroupBytes);
 #pragma unroll
         for (int ch = 0; ch < 3; ++ch) {
-          const uint32_t shift = (tcl::chunk_start(ch) >> 3) * tcl::kColGroupBytes;
-          // MN-major view: K direction = row groups, M direction = column groups
+          // advancing the 14-bit start-address field by whole 16-byte units
+          const uint64_t shift = (uint64_t)(((tcl::chunk_start(ch) >> 3) * tcl::kColGroupBytes) >> 4);
           if (mask & 2) {
-            tc::mma_bf16(tmem + kColK + ch * NK,
-                         tc::smem_desc(aChi + shift, tcl::kRowGroupBytes, tcl::kColGroupBytes), dQz,
-                         idK, false);
-            tc::mma_bf16(tmem + kColK + ch * NK,
-                         tc::smem_desc(aClo + shift, tcl::kRowGroupBytes, tcl::kColGroupBytes), dQz,
-                         idK, true);
+            tc::mma_bf16(tmem + kColK + ch * NK, mnChi + shift, dQz, idK, false);
+            tc::mma_bf16(tmem + kColK + ch * NK, mnClo + shift, dQz, idK, true);
           }
           if (mask & 4) {
-            const uint64_t dPhi =
-                tc::smem_desc(aPhi + shift, tcl::kRowGroupBytes, tcl::kColGroupBytes);
-            tc::mma_bf16(tmem + kColV + ch * NV, dPhi, dGhi, idV, false);
-            tc::mma_bf16(tmem + kColV + ch * NV,
-                         tc::smem_desc(aPlo + shift, tcl::kRowGroupBytes, tcl::kColGroupBytes), dGhi,
-                         idV, true);
-            if (has_glo) tc::mma_bf16(tmem + kColV + ch * NV, dPhi, dGlo, idV, true);
+            tc::mma_bf16(tmem + kColV + ch * NV, mnPhi + shift, dGhi, idV, false);
+            tc::mma_bf16(tmem + kColV + ch * NV, mnPlo + shift, dGhi, idV, true);
+            if (has_glo) tc::mma_bf16(tmem + kColV + ch * NV, mnPhi + shift, dGlo, idV, true);
           }
         }
         if (mask & 1) {
-          // K-major view: K direction = column groups (two per k-step), M direction = row groups
+          // K-major view (row sums): K direction = column groups, M direction = row groups
+          const uint64_t kChi = tc::smem_desc(aChi, tcl::kColGroupBytes, tcl::kRowGroupBytes);
+          const uint64_t kClo = tc::smem_desc(aClo, tcl::kColGroupBytes, tcl::kRowGroupBytes);
           const uint32_t aKz = tc::smem_addr(bKz);
+          const int g0 = (jwin + (1 << 20)) >> 4;
+          int sl = g0 % L::kKzSlots;
+#pragma unroll 1
           for (int ks = 0; ks < kWinCols / 16; ++ks) {
-            const uint64_t dKz = tc::smem_desc(aKz + ks * 2 * (NK / 8 * 128), NK / 8 * 128, 128);
-            const uint32_t shift = ks * 2 * tcl::kColGroupBytes;
-            tc::mma_bf16(tmem + kColQ,
-                         tc::smem_desc(aChi + shift, tcl::kColGroupBytes, tcl::kRowGroupBytes), dKz,
-                         idQ, ks > 0);
-            tc::mma_bf16(tmem + kColQ,
-                         tc::smem_desc(aClo + shift, tcl::kColGroupBytes, tcl::kRowGroupBytes), dKz,
-                         idQ, true);
+            const uint64_t dKz = tc::smem_desc(aKz + sl * L::kKzSlotBytes, NK / 8 * 128, 128);
+            const uint64_t shift = (uint64_t)((ks * 2 * tcl::kColGroupBytes) >> 4);
+            tc::mma_bf16(tmem + kColQ, kChi + shift, dKz, idQ, ks > 0);
+            tc::mma_bf16(tmem + kColQ, kClo + shift, dKz, idQ, true);
+            sl = sl + 1 == L::kKzSlots ? 0 : sl + 1;
           }
         }
         tc::mma_commit(mbar);
       }
-      // bounded wait: a lost completion sets a flag instead of hanging the GPU
-      if (!tc::mbar_wait(mbar, mma_phase, 1u << 24)) mma_timed_out = true;
-      mma_phase ^= 1u;
-      tc::fence_after_thread_sync();
-      // ---- epilogue: accumulators -> per-item partial gradients (this CTA owns them)
-      {
-        const int quarter = warp & 3;
-        const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
-        const bool k_half = warp < 4;
-        if (k_half ? (mask & 2) != 0 : (mask & 4) != 0) {
-#pragma unroll
-          for (int ch = 0; ch < 3; ++ch) {
-            const int c = tcl::chunk_start(ch) + 32 * quarter + lane;
-            const int j = jwin0 + c;
-            const bool use = (ch < 2 || c >= 256) && c < nrows + kVjpBand - 1 && j >= 0 &&
-                             j <= it.len - 1 - dmin;
-            const int i_top = min(j + dmax, it.len - 1);
-            const bool first = (w == it.w_begin) && (rb == i_top / kVjpRows);
-            constexpr int N = NK > NV ? NK : NV;
-            const int n = k_half ? NK : NV;
-            const int dim = k_half ? D : Dv;
-            for (int n0 = 0; n0 < n && n0 < N; n0 += 16) {
-              float v[16];
-              tc::tmem_ld16(tmem + lane_base + (k_half ? kColK + ch * NK : kColV + ch * NV) + n0, v);
-              if (use) {
-                float* dst = k_half ? a.dk_part + (it.rowslot + j) * D + n0
-                                    : a.dv_part + (it.rowslot + j + 1) * Dv + n0;
-#pragma unroll
-                for (int d = 0; d < 16; ++d)
-                  if (n0 + d < dim) dst[d] = first ? v[d] : dst[d] + v[d];
-              }
-            }
-          }
-        }
-        if ((mask & 1) && warp == 4) {
-          for (int n0 = 0; n0 < NK; n0 += 16) {
-            float v[16];
-            tc::tmem_ld16(tmem + kColQ + n0, v);   // accumulator rows 0..31 = block rows
-            if (lane < nrows) {
-              float* dst = a.dq_part + (it.rowslot + i0 + lane) * D + n0;
-#pragma unroll
-              for (int d = 0; d < 16; ++d)
-                if (n0 + d < D) dst[d] = (w == it.w_begin) ? v[d] : dst[d] + v[d];
-            }
-          }
-        }
-      }
-      tc::fence_before_thread_sync();
+      prev.w = w; prev.rb = rb; prev.i0 = i0; prev.nrows = nrows; prev.jwin = jwin;
+      prev.dmin = dmin; prev.dmax = dmax; prev.pending = true;
+      buf ^= 1;
     }
     // leave the ring zeroed for the next band of this item
     if (ring != nullptr && ring_dirty && w + 1 < it.w_end) {
       for (int s = 0; s < ring_slots; ++s) ring[(int64_t)s * kVjpBand] = 0.0f;
     }
   }
+  if (prev.pending) epilogue(prev);
   __syncthreads();
   if (mma_timed_out && tid == 0) atomicExch(a.plan.status + 1, 1);
   if (warp == 0) tc::tmem_dealloc(tmem, kTmemCols);
@@ -1159,21 +1223,38 @@ int launch_sweep2_t(const VjpArgs& a, int items_upper, bool small_dv, cudaStream
   return 0;
 }
 
-template <int NK, int NV>
-int launch_sweep2_tc(const VjpArgs& a, int items_upper, cudaStream_t stream) {
-  const int ngroups = (a.Dv + 3) / 4;
-  size_t bytes = tcl::operand_bytes(NK, NV) +
-                 (sweep_common_floats(ngroups) + 2 * kVjpRows * kVjpBand) * sizeof(float);
+template <int NK, int NV, int NG, bool kWindowed, bool kDropout>
+int launch_sweep2_tc_t(const VjpArgs& a, int items_upper, cudaStream_t stream) {
+  size_t bytes = TcSmem<NK, NV>::kBytes +
+                 (sweep_common_floats(NG) + 2 * kVjpRows * kVjpBand) * sizeof(float);
   // the row-sum MMA reads 16 row groups from the first two tiles: keep that range inside
   // the allocation
-  const size_t over_read = tcl::kTileBytes + 16 * (size_t)tcl::kRowGroupBytes + 256;
+  const size_t over_read = tcl::kTileBytes + 16 * (size_t)tcl::kRowGroupBytes + 8192;
   if (bytes < over_read) bytes = over_read;
   const unsigned grid = (unsigned)((int64_t)items_upper * a.H);
-  ROSA_CUDA_OK(cudaFuncSetAttribute(vjp_sweep2_tc_kernel<NK, NV, true>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
-  vjp_sweep2_tc_kernel<NK, NV, true><<<grid, kVjpBand, bytes, stream>>>(a);
+  auto kernel = vjp_sweep2_tc_kernel<NK, NV, NG, kWindowed, kDropout>;
+  ROSA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  kernel<<<grid, kVjpBand, bytes, stream>>>(a);
   ROSA_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+template <int NK, int NV, int NG>
+int launch_sweep2_tc_n(const VjpArgs& a, int items_upper, cudaStream_t stream) {
+  // the window product can only be non-zero when some sequence is longer than the horizon
+  const bool windowed = a.ring_slots > 0;
+  const bool dropout = a.dropout_p > 0.0f;
+  if (windowed && dropout) return launch_sweep2_tc_t<NK, NV, NG, true, true>(a, items_upper, stream);
+  if (windowed) return launch_sweep2_tc_t<NK, NV, NG, true, false>(a, items_upper, stream);
+  if (dropout) return launch_sweep2_tc_t<NK, NV, NG, false, true>(a, items_upper, stream);
+  return launch_sweep2_tc_t<NK, NV, NG, false, false>(a, items_upper, stream);
+}
+
+template <int NK>
+int launch_sweep2_tc(const VjpArgs& a, int items_upper, cudaStream_t stream) {
+  if (a.Dv <= 8) return launch_sweep2_tc_n<NK, 16, 2>(a, items_upper, stream);
+  if (a.Dv <= 16) return launch_sweep2_tc_n<NK, 16, 4>(a, items_upper, stream);
+  return launch_sweep2_tc_n<NK, 32, 8>(a, items_upper, stream);
 }
 
 template <int DPAD>
@@ -1241,10 +1322,8 @@ int launch_vjp_sweep2(const VjpArgs& a, int items_upper, cudaStream_t stream) {
   ProfileScope prof("vjp_sweep2", stream);
   if (a.Dv <= 32 && !a.force_cuda_core_contraction) {
     // tensor-core contraction (tcgen05): operand N is 16 or 32 for both symbol and value dims
-    if (a.D <= 16 && a.Dv <= 16) return launch_sweep2_tc<16, 16>(a, items_upper, stream);
-    if (a.D <= 16) return launch_sweep2_tc<16, 32>(a, items_upper, stream);
-    if (a.Dv <= 16) return launch_sweep2_tc<32, 16>(a, items_upper, stream);
-    return launch_sweep2_tc<32, 32>(a, items_upper, stream);
+    if (a.D <= 16) return launch_sweep2_tc<16>(a, items_upper, stream);
+    return launch_sweep2_tc<32>(a, items_upper, stream);
   }
   if (a.D <= 4) return launch_sweep2_d<4>(a, items_upper, stream);
   if (a.D <= 8) return launch_sweep2_d<8>(a, items_upper, stream);
