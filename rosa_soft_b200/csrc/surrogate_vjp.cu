@@ -854,15 +854,15 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   const float4* __restrict__ rowstat = a.rowstat + (int64_t)it.h * a.N + it.start;
   float* ring = ring_slots ? a.ring + it.item_linear * (int64_t)ring_slots * kVjpBand + tid
                            : nullptr;
-  constexpr uint32_t kTmemCols = (4 * NK + 3 * NV) <= 128 ? 128 : 256;
-  constexpr uint32_t kColK = 0, kColV = 3 * NK, kColQ = 3 * NK + 3 * NV;
+  constexpr uint32_t kTmemCols = (5 * NK + 3 * NV) <= 128 ? 128 : 256;
+  constexpr uint32_t kColK = 0, kColV = 3 * NK, kColQ = 3 * NK + 3 * NV, kColQ2 = kColQ + NK;
 
   // ---- one-time set-up
   for (int e = tid; e < 4 * tcl::kTileBytes / 16; e += kVjpBand)
     reinterpret_cast<uint4*>(tChi)[e] = make_uint4(0, 0, 0, 0);
   if (tid <= D) sm.glut[tid] = expf(neg_md * (float)tid);
   if (warp == 0) tc::tmem_alloc(tmem_ptr, kTmemCols);
-  if (tid == 0) tc::mbar_init(mbar, 1);
+  if (tid == 0) tc::mbar_init(mbar, 4);   // four issuing threads commit per block
   tc::fence_before_thread_sync();
   __syncthreads();
   tc::fence_after_thread_sync();
@@ -910,13 +910,14 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     }
     if ((mask & 1) && warp == 4) {
       for (int n0 = 0; n0 < NK; n0 += 16) {
-        float v[16];
+        float v[16], v2[16];
         tc::tmem_ld16(tmem + kColQ + n0, v);   // accumulator rows 0..31 = block rows
+        tc::tmem_ld16(tmem + kColQ2 + n0, v2);
         if (lane < b.nrows) {
           float* dst = a.dq_part + (it.rowslot + b.i0 + lane) * D + n0;
 #pragma unroll
           for (int d = 0; d < 16; ++d)
-            if (n0 + d < D) dst[d] = (b.w == it.w_begin) ? v[d] : dst[d] + v[d];
+            if (n0 + d < D) dst[d] = (b.w == it.w_begin) ? v[d] + v2[d] : dst[d] + (v[d] + v2[d]);
         }
       }
     }
@@ -1037,6 +1038,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
         return scale * dlogit * (0.5f * kSqrtScale) * __frcp_rn(sq);
       };
       if (!warp_p && live == 0) {
+        // no window product is alive in this warp: P = 0, T = 0, Y = 0, C = S * Sbar
 #pragma unroll 4
         for (int r = nrows - 1; r >= 0; --r) {
           const bool act = r >= r_first;
@@ -1046,7 +1048,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
           float pd;
           const float dS = seed(act, r, c, Sv, &pd);
           Sbar = (double)dS + (double)xnext * Sbar;
-          const float Cv = act ? (float)((double)Sv * Sbar) : 0.0f;
+          const float Cv = act ? Sv * (float)Sbar : 0.0f;
           const int off = tcl::tile_off(r, c);
           tcl::store_split(tChi, tClo, off, Cv);
           tcl::store_split(tPhi, tPlo, off, pd);
@@ -1099,48 +1101,57 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
       tc::fence_proxy_async_smem();
       tc::fence_before_thread_sync();
       __syncthreads();                                                    // sync 2
-      if (tid == 0) {
+      // Four issuing threads (lane 0 of warps 0..3) share the work so that no single warp
+      // falls behind the others at the next barrier: column sums of C, column sums of p*d,
+      // and the two halves of the row-sum k-loop (separate accumulators, added in the
+      // epilogue).  Each issuer commits once; the mbarrier expects four arrivals.
+      if (lane == 0 && warp < 4) {
         tc::fence_after_thread_sync();
-        const uint32_t aChi = tc::smem_addr(tChi), aClo = tc::smem_addr(tClo);
-        const uint32_t aPhi = tc::smem_addr(tPhi), aPlo = tc::smem_addr(tPlo);
         constexpr uint32_t idK = tc::idesc_bf16_f32(128, NK, true, false);
         constexpr uint32_t idV = tc::idesc_bf16_f32(128, NV, true, false);
         constexpr uint32_t idQ = tc::idesc_bf16_f32(128, NK, false, false);
-        const uint64_t dQz = tc::smem_desc(tc::smem_addr(bQz), NK / 8 * 128, 128);
-        const uint64_t dGhi = tc::smem_desc(tc::smem_addr(bGhi), NV / 8 * 128, 128);
-        const uint64_t dGlo = tc::smem_desc(tc::smem_addr(bGlo), NV / 8 * 128, 128);
-        // MN-major view (column sums): K direction = row groups, M direction = column groups
-        const uint64_t mnChi = tc::smem_desc(aChi, tcl::kRowGroupBytes, tcl::kColGroupBytes);
-        const uint64_t mnClo = tc::smem_desc(aClo, tcl::kRowGroupBytes, tcl::kColGroupBytes);
-        const uint64_t mnPhi = tc::smem_desc(aPhi, tcl::kRowGroupBytes, tcl::kColGroupBytes);
-        const uint64_t mnPlo = tc::smem_desc(aPlo, tcl::kRowGroupBytes, tcl::kColGroupBytes);
+        if (warp == 0 && (mask & 2)) {
+          const uint64_t dQz = tc::smem_desc(tc::smem_addr(bQz), NK / 8 * 128, 128);
+          // MN-major view (column sums): K direction = row groups, M direction = column groups
+          const uint64_t mnChi = tc::smem_desc(tc::smem_addr(tChi), tcl::kRowGroupBytes, tcl::kColGroupBytes);
+          const uint64_t mnClo = tc::smem_desc(tc::smem_addr(tClo), tcl::kRowGroupBytes, tcl::kColGroupBytes);
 #pragma unroll
-        for (int ch = 0; ch < 3; ++ch) {
-          // advancing the 14-bit start-address field by whole 16-byte units
-          const uint64_t shift = (uint64_t)(((tcl::chunk_start(ch) >> 3) * tcl::kColGroupBytes) >> 4);
-          if (mask & 2) {
+          for (int ch = 0; ch < 3; ++ch) {
+            // advancing the 14-bit start-address field by whole 16-byte units
+            const uint64_t shift = (uint64_t)(((tcl::chunk_start(ch) >> 3) * tcl::kColGroupBytes) >> 4);
             tc::mma_bf16(tmem + kColK + ch * NK, mnChi + shift, dQz, idK, false);
             tc::mma_bf16(tmem + kColK + ch * NK, mnClo + shift, dQz, idK, true);
           }
-          if (mask & 4) {
+        }
+        if (warp == 1 && (mask & 4)) {
+          const uint64_t dGhi = tc::smem_desc(tc::smem_addr(bGhi), NV / 8 * 128, 128);
+          const uint64_t dGlo = tc::smem_desc(tc::smem_addr(bGlo), NV / 8 * 128, 128);
+          const uint64_t mnPhi = tc::smem_desc(tc::smem_addr(tPhi), tcl::kRowGroupBytes, tcl::kColGroupBytes);
+          const uint64_t mnPlo = tc::smem_desc(tc::smem_addr(tPlo), tcl::kRowGroupBytes, tcl::kColGroupBytes);
+#pragma unroll
+          for (int ch = 0; ch < 3; ++ch) {
+            const uint64_t shift = (uint64_t)(((tcl::chunk_start(ch) >> 3) * tcl::kColGroupBytes) >> 4);
             tc::mma_bf16(tmem + kColV + ch * NV, mnPhi + shift, dGhi, idV, false);
             tc::mma_bf16(tmem + kColV + ch * NV, mnPlo + shift, dGhi, idV, true);
             if (has_glo) tc::mma_bf16(tmem + kColV + ch * NV, mnPhi + shift, dGlo, idV, true);
           }
         }
-        if (mask & 1) {
+        if (warp >= 2 && (mask & 1)) {
           // K-major view (row sums): K direction = column groups, M direction = row groups
-          const uint64_t kChi = tc::smem_desc(aChi, tcl::kColGroupBytes, tcl::kRowGroupBytes);
-          const uint64_t kClo = tc::smem_desc(aClo, tcl::kColGroupBytes, tcl::kRowGroupBytes);
-          const uint32_t aKz = tc::smem_addr(bKz);
+          const uint64_t kChi = tc::smem_desc(tc::smem_addr(tChi), tcl::kColGroupBytes, tcl::kRowGroupBytes);
+          const uint64_t kClo = tc::smem_desc(tc::smem_addr(tClo), tcl::kColGroupBytes, tcl::kRowGroupBytes);
+          const uint64_t dKz0 = tc::smem_desc(tc::smem_addr(bKz), NK / 8 * 128, 128);
+          constexpr int kSteps = kWinCols / 16, kHalf = (kSteps + 1) / 2;
+          const int ks0 = warp == 2 ? 0 : kHalf, ks1 = warp == 2 ? kHalf : kSteps;
+          const uint32_t acc = tmem + (warp == 2 ? kColQ : kColQ2);
           const int g0 = (jwin + (1 << 20)) >> 4;
-          int sl = g0 % L::kKzSlots;
+          int sl = (g0 + ks0) % L::kKzSlots;
 #pragma unroll 1
-          for (int ks = 0; ks < kWinCols / 16; ++ks) {
-            const uint64_t dKz = tc::smem_desc(aKz + sl * L::kKzSlotBytes, NK / 8 * 128, 128);
+          for (int ks = ks0; ks < ks1; ++ks) {
+            const uint64_t dKz = dKz0 + (uint64_t)((sl * L::kKzSlotBytes) >> 4);
             const uint64_t shift = (uint64_t)((ks * 2 * tcl::kColGroupBytes) >> 4);
-            tc::mma_bf16(tmem + kColQ, kChi + shift, dKz, idQ, ks > 0);
-            tc::mma_bf16(tmem + kColQ, kClo + shift, dKz, idQ, true);
+            tc::mma_bf16(acc, kChi + shift, dKz, idQ, ks > ks0);
+            tc::mma_bf16(acc, kClo + shift, dKz, idQ, true);
             sl = sl + 1 == L::kKzSlots ? 0 : sl + 1;
           }
         }
