@@ -301,10 +301,12 @@ __device__ __forceinline__ bool load_item_1d(const VjpArgs& a, Item* o) {
 // kFixedRef: the row reference of the online softmax is the analytic upper bound of the
 // logits (valid while scale * c * (sqrt(1 + W) - 1) stays far inside the float exponent
 // range), so no maximum has to be reduced and four rows share one transposing reduction.
-template <bool kSmallDv, bool kFixedRef>
+// NG: number of 4-wide value groups (compile time) when Dv <= 32, 0 for the generic path.
+template <int NG, bool kFixedRef, bool kWindowed, bool kDropout>
 __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
+  constexpr bool kSmallDv = NG > 0;
   extern __shared__ float4 smem_raw[];
-  const int ngroups = kSmallDv ? (a.Dv + 3) / 4 : 0;
+  const int ngroups = NG;
   SweepSmem sm = carve_common(reinterpret_cast<float*>(smem_raw), ngroups);
   Item it;
   if (!load_item_1d(a, &it)) return;
@@ -319,12 +321,40 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
   const int W = a.W;
   const float scale = a.scale, inv_keep = a.inv_keep;
   const float neg_md = -a.mismatch_scale / (float)a.D;
-  const bool windowed = W <= it.len - 2;
-  const bool use_dropout = a.dropout_p > 0.0f;
+  constexpr bool windowed = kWindowed;
+  constexpr bool use_dropout = kDropout;
   const DropoutKey dkey = make_dropout_key((uint32_t)it.h + a.head_offset,
                                            (uint32_t)it.seq + a.batch_offset, a.seed, a.dropout_p);
   const float ref_top = scale * kSqrtScale * (sqrtf(1.0f + (float)W) - 1.0f);
+  const float logit_mul = kSqrtScale * scale;
   if (tid <= a.D) sm.glut[tid] = expf(neg_md * (float)tid);
+
+  // one cell of the forward sweep: returns (e, e * d * u) and, with dropout, the keep flag
+  auto cell = [&](bool act, int r, int c, int j, int i, float& S, int& hs, float& e, float& edu,
+                  bool& keep) {
+    forward_cell(S, hs, act, sm.s_q[r], sm.s_k[c], sm.s_qold[r], sm.s_kold[c], j, sm.glut,
+                 windowed, W, neg_md);
+    // the log i term cancels in the softmax, so the fixed reference drops it too
+    const float logit = (sqrtf(1.0f + S) - 1.0f) * logit_mul - ref_top;
+    const float ex = __expf(logit);
+    e = act ? ex : 0.0f;
+    float du;
+    if (kSmallDv) {
+      const uint32_t bits = sm.s_vb[c];
+      const float* lut = sm.ulut + r * NG * 16;
+      du = 0.0f;
+#pragma unroll
+      for (int g = 0; g < NG; ++g) du += lut[g * 16 + ((bits >> (4 * g)) & 15u)];
+    } else {
+      du = act ? route_utility<false>(a, it, vb, i, r, j + 1, ngroups, sm.ulut) : 0.0f;
+    }
+    keep = true;
+    if (kDropout) {
+      keep = act && dropout_keep_from_route(dkey, sm.s_h1[c], (uint32_t)i);
+      du = keep ? du * inv_keep : 0.0f;
+    }
+    edu = e * du;
+  };
 
   for (int w = it.w_begin; w < it.w_end; ++w) {
     const int dmin = 1 + w * kVjpBand;
@@ -352,39 +382,51 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
       const int r_first = valid ? max(0, delta - i0) : nrows;
       const int cbase = kVjpBand - 1 - tid;   // column window index on block row 0
       const int jbase = i0 - delta;           // key column on block row 0
+      const int vslot = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
 
-      if (kFixedRef) {
+      if (kFixedRef && nrows == kVjpRows) {
+        // full block: four rows per transposing reduction, no tail handling
+#pragma unroll 1
+        for (int r0 = 0; r0 < kVjpRows; r0 += 4) {
+          float v[8];
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            const int r = r0 + rr;
+            bool keep;
+            cell(r >= r_first, r, cbase + r, jbase + r, i0 + r, S, hs, v[2 * rr], v[2 * rr + 1],
+                 keep);
+            if (kDropout) {
+              const uint32_t bits = __ballot_sync(0xffffffffu, keep);
+              if (lane == 0) keep_out[r * kVjpWarps] = bits;
+            }
+          }
+          const float total = warp_reduce8(v, lane);
+          if ((lane & 3) == 0)
+            reinterpret_cast<float*>(sm.wstat + (r0 + (vslot >> 1)) * kVjpWarps + warp)[1 + (vslot & 1)] =
+                total;
+        }
+      } else if (kFixedRef) {
         for (int r0 = 0; r0 < nrows; r0 += 4) {
           float v[8];
 #pragma unroll
           for (int rr = 0; rr < 4; ++rr) {
             const int r = min(r0 + rr, nrows - 1);       // clamped: the tail repeats a row, masked
-            const bool act = r0 + rr < nrows && r >= r_first;
-            const int c = cbase + r, j = jbase + r, i = i0 + r;
-            if (r0 + rr < nrows)
-              forward_cell(S, hs, act, sm.s_q[r], sm.s_k[c], sm.s_qold[r], sm.s_kold[c], j,
-                           sm.glut, windowed, W, neg_md);
-            const float logit = kSqrtScale * (sqrtf(1.0f + S) - 1.0f) * scale - ref_top;
-            const float e = act ? __expf(logit) : 0.0f;   // the log i term cancels in the softmax
-            float du = cell_utility<kSmallDv>(a, it, sm, vb, act, i, j, r, c, ngroups);
-            if (use_dropout) {
-              const bool keep =
-                  act && dropout_keep_from_route(dkey, sm.s_h1[c], (uint32_t)i);
-              const uint32_t bits = __ballot_sync(0xffffffffu, keep);
-              if (lane == 0 && r0 + rr < nrows) keep_out[r * kVjpWarps] = bits;
-              du = keep ? du * inv_keep : 0.0f;
+            const bool in = r0 + rr < nrows;
+            bool keep = false;
+            float e = 0.0f, edu = 0.0f;
+            if (in) cell(r >= r_first, r, cbase + r, jbase + r, i0 + r, S, hs, e, edu, keep);
+            if (kDropout) {
+              const uint32_t bits = __ballot_sync(0xffffffffu, in && keep);
+              if (lane == 0 && in) keep_out[r * kVjpWarps] = bits;
             }
             v[2 * rr] = e;
-            v[2 * rr + 1] = e * du;
+            v[2 * rr + 1] = edu;
           }
           const float total = warp_reduce8(v, lane);
           if ((lane & 3) == 0) {
-            const int idx = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-            const int r = r0 + (idx >> 1);
-            if (r < nrows) {
-              float* dst = reinterpret_cast<float*>(sm.wstat + r * kVjpWarps + warp);
-              dst[1 + (idx & 1)] = total;
-            }
+            const int r = r0 + (vslot >> 1);
+            if (r < nrows)
+              reinterpret_cast<float*>(sm.wstat + r * kVjpWarps + warp)[1 + (vslot & 1)] = total;
           }
         }
       } else {
@@ -1307,14 +1349,29 @@ int launch_vjp_sweep1(const VjpArgs& a, int items_upper, cudaStream_t stream) {
   // float exponent range; otherwise every row reduces its own maximum
   const float top = a.scale * kSqrtScale * (sqrtf(1.0f + (float)a.W) - 1.0f);
   const bool fixed_ref = top <= 80.0f;
-  if (small_dv && fixed_ref)
-    vjp_sweep1_kernel<true, true><<<grid, kVjpBand, bytes, stream>>>(a);
-  else if (small_dv)
-    vjp_sweep1_kernel<true, false><<<grid, kVjpBand, bytes, stream>>>(a);
-  else if (fixed_ref)
-    vjp_sweep1_kernel<false, true><<<grid, kVjpBand, bytes, stream>>>(a);
-  else
-    vjp_sweep1_kernel<false, false><<<grid, kVjpBand, bytes, stream>>>(a);
+  const bool windowed = a.ring_slots > 0;     // some sequence may be longer than the horizon
+  const bool dropout = a.dropout_p > 0.0f;
+  const int ng = !small_dv ? 0 : a.Dv <= 8 ? 2 : a.Dv <= 16 ? 4 : 8;
+  const size_t smem = sweep_common_floats(ng) * sizeof(float);
+#define ROSA_SWEEP1(NGV, FR, WI, DO)                                                        \
+  vjp_sweep1_kernel<NGV, FR, WI, DO><<<grid, kVjpBand, smem, stream>>>(a)
+#define ROSA_SWEEP1_FLAGS(NGV)                                                              \
+  do {                                                                                      \
+    if (fixed_ref) {                                                                        \
+      if (windowed) { if (dropout) ROSA_SWEEP1(NGV, true, true, true); else ROSA_SWEEP1(NGV, true, true, false); } \
+      else          { if (dropout) ROSA_SWEEP1(NGV, true, false, true); else ROSA_SWEEP1(NGV, true, false, false); } \
+    } else {                                                                                \
+      if (windowed) { if (dropout) ROSA_SWEEP1(NGV, false, true, true); else ROSA_SWEEP1(NGV, false, true, false); } \
+      else          { if (dropout) ROSA_SWEEP1(NGV, false, false, true); else ROSA_SWEEP1(NGV, false, false, false); } \
+    }                                                                                       \
+  } while (0)
+  if (ng == 0) ROSA_SWEEP1_FLAGS(0);
+  else if (ng == 2) ROSA_SWEEP1_FLAGS(2);
+  else if (ng == 4) ROSA_SWEEP1_FLAGS(4);
+  else ROSA_SWEEP1_FLAGS(8);
+#undef ROSA_SWEEP1_FLAGS
+#undef ROSA_SWEEP1
+  (void)bytes;
   ROSA_CUDA_OK(cudaGetLastError());
   return 0;
 }
