@@ -925,27 +925,43 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     const bool k_half = warp < 4;
     const int ncols = b.nrows + kVjpBand - 1 + (b.i0 - b.rb * kVjpRows);
     if (k_half ? (mask & 2) != 0 : (mask & 4) != 0) {
+      const int ncol = k_half ? NK : NV;
+      const int dim = k_half ? D : Dv;
+      float* part = k_half ? a.dk_part + it.rowslot * D : a.dv_part + (it.rowslot + 1) * Dv;
+      const bool vec4 = (dim & 3) == 0;
 #pragma unroll
       for (int ch = 0; ch < 3; ++ch) {
+        // only window columns >= 256 of the last chunk are new: they sit in the last quarter
+        if (ch == 2 && quarter < 3) continue;
         const int c = tcl::chunk_start(ch) + 32 * quarter + lane;
         const int j = b.jwin + c;
         const bool use =
             (ch < 2 || c >= 256) && c < ncols && j >= 0 && j <= it.len - 1 - b.dmin;
         const int i_top = min(j + b.dmax, it.len - 1);
         const bool first = (b.w == it.w_begin) && (b.rb == i_top / kVjpRows);
-        constexpr int n = NK;   // placate unused warnings when NK == NV
-        (void)n;
-        const int ncol = k_half ? NK : NV;
-        const int dim = k_half ? D : Dv;
-        for (int n0 = 0; n0 < ncol; n0 += 16) {
+        for (int n0 = 0; n0 < ncol && n0 < dim; n0 += 16) {
           float v[16];
           tc::tmem_ld16(tmem + lane_base + (k_half ? kColK + ch * NK : kColV + ch * NV) + n0, v);
           if (use) {
-            float* dst = k_half ? a.dk_part + (it.rowslot + j) * D + n0
-                                : a.dv_part + (it.rowslot + j + 1) * Dv + n0;
+            float* dst = part + (int64_t)j * dim + n0;
+            if (vec4) {
 #pragma unroll
-            for (int d = 0; d < 16; ++d)
-              if (n0 + d < dim) dst[d] = first ? v[d] : dst[d] + v[d];
+              for (int d4 = 0; d4 < 4; ++d4) {
+                if (n0 + 4 * d4 < dim) {
+                  float4* p4 = reinterpret_cast<float4*>(dst) + d4;
+                  float4 o = first ? make_float4(0.f, 0.f, 0.f, 0.f) : *p4;
+                  o.x += v[4 * d4 + 0];
+                  o.y += v[4 * d4 + 1];
+                  o.z += v[4 * d4 + 2];
+                  o.w += v[4 * d4 + 3];
+                  *p4 = o;
+                }
+              }
+            } else {
+#pragma unroll
+              for (int d = 0; d < 16; ++d)
+                if (n0 + d < dim) dst[d] = first ? v[d] : dst[d] + v[d];
+            }
           }
         }
       }
