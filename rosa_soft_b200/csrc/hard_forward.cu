@@ -139,6 +139,92 @@ __global__ void __launch_bounds__(kFwdWarps * 32)
   }
 }
 
+// Fast matcher for horizons below 2048 and sequences below 2^21 tokens: the candidate of a
+// cell is one 32-bit key (run length << 21 | route), so the row winner is a plain integer
+// max.  A CTA of 256 threads owns kFwdBand diagonals (four per thread), stages the key
+// symbols of a 32-row block in shared memory, reduces the winner of a row with one
+// redux.sync per warp, merges the warps through a shared-memory atomicMax and issues at most
+// one global 64-bit atomicMax per row and block.
+constexpr int kMatchRows = 32;
+constexpr int kMatchThreads = 256;
+constexpr int kMatchPerThread = kFwdBand / kMatchThreads;   // 4
+constexpr int kMatchWin = kFwdBand + kMatchRows;
+
+template <bool kRamp>
+__device__ __forceinline__ void match_rows(int nrows, int tid, int lane, int W, int cmin,
+                                           const int* s_q, const int* s_k, unsigned* s_best,
+                                           int (&run)[kMatchPerThread], int abase) {
+  for (int r = 0; r < nrows; ++r) {
+    const int qi = s_q[r];
+    unsigned best = 0;
+#pragma unroll
+    for (int u = 0; u < kMatchPerThread; ++u) {
+      const int c = kFwdBand - 1 - tid - u * kMatchThreads + r;   // window column of this cell
+      bool eq = s_k[c] == qi;
+      if (kRamp) eq = eq && c >= cmin;                            // columns before the sequence
+      const int l = eq ? min(run[u] + 1, W) : 0;
+      run[u] = l;
+      const unsigned key = ((unsigned)l << 21) + (unsigned)(abase + c);   // route = jwin0 + c + 1
+      if (eq) best = max(best, key);
+    }
+    const unsigned wbest = __reduce_max_sync(0xffffffffu, best);
+    if (lane == 0 && wbest > 0) atomicMax(s_best + r, wbest);
+  }
+}
+
+__global__ void __launch_bounds__(kMatchThreads)
+    hard_match_fast_kernel(Plan plan, const int32_t* __restrict__ qsym,
+                           const int32_t* __restrict__ ksym, int64_t sym_seq_stride,
+                           int64_t sym_head_stride, int H, int W,
+                           unsigned long long* __restrict__ best) {
+  __shared__ int s_k[kMatchWin];
+  __shared__ int s_q[kMatchRows];
+  __shared__ unsigned s_best[kMatchRows];
+  const int slot = blockIdx.x / H;
+  int seq, local;
+  if (!find_item(plan, slot, &seq, &local)) return;
+  const int h = blockIdx.x - slot * H;
+  const int start = plan.seg_start[seq];
+  const int len = plan.seg_len[seq];
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int dmin = 1 + local * kFwdBand, dmax = dmin + kFwdBand - 1;
+  const bool dense = plan.cu_seqlens == nullptr;
+  const int64_t sym_base =
+      (int64_t)seq * sym_seq_stride + (int64_t)h * sym_head_stride + (dense ? 0 : start);
+  const int32_t* __restrict__ q = qsym + sym_base;
+  const int32_t* __restrict__ k = ksym + sym_base;
+  int run[kMatchPerThread];
+#pragma unroll
+  for (int u = 0; u < kMatchPerThread; ++u) run[u] = 0;
+
+  for (int i0 = dmin; i0 < len; i0 = (i0 / kMatchRows + 1) * kMatchRows) {
+    const int i1 = min((i0 / kMatchRows + 1) * kMatchRows - 1, len - 1);
+    const int nrows = i1 - i0 + 1;
+    const int jwin0 = i0 - dmax;   // key column of window index 0
+    __syncthreads();
+    for (int c = tid; c < nrows + kFwdBand - 1; c += kMatchThreads) {
+      const int j = jwin0 + c;
+      s_k[c] = (j >= 0 && j < len - 1) ? __ldg(k + j) : 0;
+    }
+    if (tid < nrows) {
+      s_q[tid] = __ldg(q + i0 + tid);
+      s_best[tid] = 0;
+    }
+    __syncthreads();
+    if (jwin0 < 0)
+      match_rows<true>(nrows, tid, lane, W, -jwin0, s_q, s_k, s_best, run, jwin0 + 1);
+    else
+      match_rows<false>(nrows, tid, lane, W, 0, s_q, s_k, s_best, run, jwin0 + 1);
+    __syncthreads();
+    if (tid < nrows && s_best[tid] > 0) {
+      const unsigned key = s_best[tid];
+      const unsigned long long wide =
+          ((unsigned long long)(key >> 21) << 32) | (unsigned long long)(key & 0x1FFFFFu);
+      atomicMax(best + ((int64_t)(start + i0 + tid) * H + h), wide);
+    }
+  }
+}
+
 // ------------------------------------------------------------------- gather
 template <typename T>
 __device__ __forceinline__ T from_float(float x);
@@ -235,6 +321,14 @@ int launch_transpose_symbols(const uint32_t* q, const uint32_t* k, int64_t N, in
 int launch_hard_match(const FwdArgs& a, int items_upper, cudaStream_t stream) {
   if (items_upper <= 0) return 0;
   ProfileScope prof("hard_match", stream);
+  const int64_t max_len = a.plan.cu_seqlens == nullptr ? a.plan.uniform_len : a.N;
+  if (a.W < 2048 && max_len < (1 << 21)) {
+    // 32-bit candidate keys: run length in the top 11 bits, route in the low 21
+    hard_match_fast_kernel<<<(unsigned)((int64_t)items_upper * a.H), kMatchThreads, 0, stream>>>(
+        a.plan, a.packed_q, a.packed_k, a.sym_seq_stride, a.sym_head_stride, a.H, a.W, a.best);
+    ROSA_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
   dim3 grid((unsigned)items_upper, (unsigned)a.H);
   hard_match_kernel<<<grid, kFwdWarps * 32, 0, stream>>>(a.plan, a.packed_q, a.packed_k,
                                                         a.sym_seq_stride, a.sym_head_stride, a.H,
