@@ -40,11 +40,55 @@ WORKLOADS = {
     # a case small enough for a full-metric profiler capture whose scratch still exceeds L2
     "profile": dict(B=1, T=4096, H=32, D=8, Hv=8, Dv=8, W=128, scale=1.0, p=0.1, m=3.0,
                     dtype="bfloat16", gen="randn"),
+    # packed variable-length case: 32768 tokens in sequences of 64..4096 tokens
+    "c4": dict(kind="varlen", N=32768, Lmin=64, Lmax=4096, B=1, T=32768, H=32, D=16, Hv=8, Dv=32,
+               W=64, scale=1.0, p=0.05, m=9.0, dtype="float16", gen="randn"),
+    # batched hard inference: 64 streams x 16384 tokens x 64 heads of 32-bit symbols, forward only
+    "c5": dict(kind="inference", B=64, T=16384, H=64, D=32, Hv=64, Dv=8, W=32, scale=1.0, p=0.0,
+               m=3.0, dtype="float32", gen="symbols"),
     "small": dict(B=1, T=1024, H=8, D=8, Hv=2, Dv=8, W=128, scale=1.0, p=0.1, m=3.0,
                   dtype="bfloat16", gen="randn"),
 }
 # bounded CPU sample of a workload: same D/Dv/W/controls, fewer heads and a shorter sequence
-CPU_SAMPLE = dict(B=1, T=1024, H=32)
+CPU_SAMPLE = dict(B=1, T=2048, H=64)
+
+
+def varlen_lengths(cfg, seed):
+    """Sequence lengths uniform in [Lmin, Lmax] until the token budget is used (last one cut)."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    lengths, total = [], 0
+    while total < cfg["N"]:
+        n = min(int(rng.integers(cfg["Lmin"], cfg["Lmax"] + 1)), cfg["N"] - total)
+        lengths.append(n)
+        total += n
+    return lengths
+
+
+def make_inference_inputs(cfg, seed, device):
+    """i.i.d. 32-bit symbols; 10 % of the positions start a copy of an earlier window of 8..512
+    symbols into both streams, so that long matches exist."""
+    import numpy as np
+    import torch
+
+    rng = np.random.default_rng(seed)
+    B, T, H = cfg["B"], cfg["T"], cfg["H"]
+    k = rng.integers(0, 1 << 32, size=(B, T, H), dtype=np.uint64).astype(np.uint32)
+    q = rng.integers(0, 1 << 32, size=(B, T, H), dtype=np.uint64).astype(np.uint32)
+    for b in range(B):
+        t = 600
+        while t < T - 520:
+            if rng.random() < 0.1:
+                n = int(rng.integers(8, 513))
+                src = int(rng.integers(0, t - n))
+                k[b, t:t + n] = k[b, src:src + n]
+                q[b, t + 1:t + 1 + n] = k[b, src + 1:src + 1 + n]
+                t += n
+            t += int(rng.integers(1, 20))
+    payload = rng.standard_normal((B, T, cfg["Hv"], cfg["Dv"])).astype(np.float32)
+    to = lambda a: torch.from_numpy(a).to(device)
+    return to(q.view(np.int32)), to(k.view(np.int32)), to(payload)
 
 
 def make_inputs(cfg, seed, device, dtype):
@@ -132,6 +176,24 @@ def cpu_reference_run(cfg, steps, warmup):
 
     from oracle import rosa_oracle as orc
 
+    if cfg.get("kind") == "inference":
+        sample = dict(cfg, B=4, T=4096, H=8, Hv=8)
+        qs, ks, pay = (t.numpy() for t in make_inference_inputs(sample, 7, "cpu"))
+        B, T, H = sample["B"], sample["T"], sample["H"]
+        cu = np.arange(B + 1, dtype=np.int64) * T
+        flat = lambda a: a.reshape((B * T,) + a.shape[2:])
+        times = []
+        for it in range(warmup + steps):
+            t0 = time.perf_counter()
+            orc.hard_inference(flat(qs).view(np.uint32), flat(ks).view(np.uint32), flat(pay), cu,
+                               sample["W"])
+            if it >= warmup:
+                times.append(time.perf_counter() - t0)
+        sec = sum(times) / len(times)
+        desc = (f"{B} streams x T={T} x H={H} of the workload (quadratic run-length matcher; cost per "
+                f"token-head grows with T)")
+        return B * T * H / sec / 1e6, sec, orc.num_threads(), desc
+
     sample = dict(cfg, **{k: min(cfg[k], v) for k, v in CPU_SAMPLE.items()})
     sample["Hv"] = max(1, sample["H"] // (cfg["H"] // cfg["Hv"]))
     q, k, v, go = (t.float().numpy() for t in make_inputs(sample, 7, None, torch.float32))
@@ -203,21 +265,44 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     dtype = getattr(torch, cfg["dtype"])
-    q, k, v, go = make_inputs(cfg, 1000 + rank, dev, dtype)
-    for t in (q, k, v):
-        t.requires_grad_(True)
+    kind = cfg.get("kind", "dense")
     kw = dict(max_suffix_length=cfg["W"], scale=cfg["scale"], dropout_p=cfg["p"], mismatch_scale=cfg["m"])
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    if kind == "inference":
+        inputs = list(make_inference_inputs(cfg, 1000 + rank, dev))
+        pairs = cfg["B"] * cfg["H"] * cfg["T"] * (cfg["T"] - 1) // 2
 
-    def step(qq, kk, vv, gg):
-        for t in (qq, kk, vv):
-            t.grad = None
-        out = rs.rosa_soft(qq, kk, vv, **kw)
-        out.backward(gg)
-        return out
+        def step(qs, ks, pay):
+            return list(rs.rosa_hard_inference(qs, ks, pay, max_suffix_length=cfg["W"]))
+    elif kind == "varlen":
+        lengths = varlen_lengths(cfg, 1004)
+        cu = torch.tensor([0] + list(__import__("itertools").accumulate(lengths)), dtype=torch.int32,
+                          device=dev)
+        inputs = [t.squeeze(0).contiguous() for t in make_inputs(cfg, 1000 + rank, dev, dtype)]
+        pairs = cfg["H"] * sum(n * (n - 1) // 2 for n in lengths)
+        config["sequence_lengths"] = lengths
+
+        def step(qq, kk, vv, gg):
+            for t in (qq, kk, vv):
+                t.grad = None
+                t.requires_grad_(True)
+            out = rs.rosa_soft_varlen(qq, kk, vv, cu, **kw)
+            out.backward(gg)
+            return [out.detach(), qq.grad, kk.grad, vv.grad]
+    else:
+        inputs = make_inputs(cfg, 1000 + rank, dev, dtype)
+        pairs = cfg["B"] * cfg["H"] * cfg["T"] * (cfg["T"] - 1) // 2
+
+        def step(qq, kk, vv, gg):
+            for t in (qq, kk, vv):
+                t.grad = None
+                t.requires_grad_(True)
+            out = rs.rosa_soft(qq, kk, vv, **kw)
+            out.backward(gg)
+            return [out.detach(), qq.grad, kk.grad, vv.grad]
 
     for _ in range(max(3, args.warmup)):
-        step(q, k, v, go)
+        step(*inputs)
     torch.cuda.synchronize()
 
     def barrier():
@@ -236,7 +321,7 @@ def main():
         for i in range(args.steps):
             flush.fill_(i)
             starts[i].record()
-            step(q, k, v, go)
+            step(*inputs)
             stops[i].record()
         barrier()
     kernels = cabi.profile_collect()
@@ -245,17 +330,14 @@ def main():
     total_ms = sum(step_ms)
 
     # ---- end to end: pinned host buffers in, results out, inside the timed region
-    host = [t.detach().cpu().pin_memory() for t in (q, k, v, go)]
-    host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (go, q, k, v)]
+    host = [t.detach().cpu().pin_memory() for t in inputs]
+    host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in step(*inputs)]
     e2e_start = torch.cuda.Event(enable_timing=True)
     e2e_stop = torch.cuda.Event(enable_timing=True)
 
     def e2e_step():
-        dq, dk, dv, dg = (h.to(dev, non_blocking=True) for h in host)
-        for t in (dq, dk, dv):
-            t.requires_grad_(True)
-        out = step(dq, dk, dv, dg)
-        for dst, src in zip(host_out, (out.detach(), dq.grad, dk.grad, dv.grad)):
+        device_inputs = [h.to(dev, non_blocking=True) for h in host]
+        for dst, src in zip(host_out, step(*device_inputs)):
             dst.copy_(src, non_blocking=True)
 
     e2e_step()
@@ -283,8 +365,9 @@ def main():
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except OSError:
         pass
-    pairs = cfg["B"] * cfg["H"] * cfg["T"] * (cfg["T"] - 1) // 2
     flop = (6 * cfg["D"] + 4 * cfg["Dv"]) * pairs           # algorithmic contraction FLOP per launch
+    if kind == "inference":
+        flop = 0
     k_ms, k_n = kernels.get("vjp_sweep2", (0.0, 0))
     k_avg_s = (k_ms / k_n / 1e3) if k_n else None
     tensor_peak = peaks.get("bf16_tflops_sustained")
@@ -293,14 +376,17 @@ def main():
         tensor_peak, peak_note = 1400.0, "fallback"
     achieved = flop / k_avg_s / 1e12 if k_avg_s else None
     s = 2 if cfg["dtype"] != "float32" else 4
-    fwd_bytes = (2 * cfg["D"] * s + cfg["Dv"] * s * cfg["Hv"] / cfg["H"] + cfg["Dv"] * s + 8) \
-        * cfg["B"] * cfg["T"] * cfg["H"]
-    fwd_ms = sum(kernels.get(n, (0.0, 0))[0] for n in ("pack_symbols", "hard_match", "gather_output"))
+    per_unit = (80 if kind == "inference" else
+                2 * cfg["D"] * s + cfg["Dv"] * s * cfg["Hv"] / cfg["H"] + cfg["Dv"] * s + 8)
+    fwd_bytes = per_unit * cfg["B"] * cfg["T"] * cfg["H"]
+    fwd_ms = sum(kernels.get(n, (0.0, 0))[0] for n in ("pack_symbols", "transpose_symbols", "hard_match",
+                                                       "gather_output", "inference_finish"))
     fwd_n = kernels.get("hard_match", (0.0, 1))[1] or 1
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
     fwd_gbs = fwd_bytes / (fwd_ms / fwd_n / 1e3) / 1e9 if fwd_ms else None
     result = {
-        "metric": "fwd+bwd M token-heads/s", "value": units * args.steps / (total_ms / 1e3) / 1e6,
+        "metric": ("forward M token-heads/s" if kind == "inference" else "fwd+bwd M token-heads/s"),
+        "value": units * args.steps / (total_ms / 1e3) / 1e6,
         "unit": "M token-heads/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 accumulate on " + cfg["dtype"] + " inputs; integer symbols",
