@@ -22,7 +22,6 @@ struct FwdLayout {
   PlanLayout plan;
   size_t best_off, qt_off, kt_off;
   size_t bytes;
-  int items_upper;
 };
 
 int64_t fwd_items_upper(int64_t N, int64_t S, int64_t uniform_len, bool dense) {

@@ -68,22 +68,6 @@ struct Item {
   int64_t item_linear;   // dense index over (sequence, head, item)
 };
 
-__device__ __forceinline__ bool load_item(const VjpArgs& a, Item* o) {
-  if (!find_item(a.plan, blockIdx.x, &o->seq, &o->it)) return false;
-  o->h = blockIdx.y;
-  o->start = a.plan.seg_start[o->seq];
-  o->len = a.plan.seg_len[o->seq];
-  o->nitems = a.plan.item_prefix[o->seq + 1] - a.plan.item_prefix[o->seq];
-  const int nbands = (int)vjp_bands(o->len);
-  o->w_begin = o->it * a.bands_per_item;
-  o->w_end = min(nbands, o->w_begin + a.bands_per_item);
-  o->rowslot = a.plan.row_prefix[o->seq] * a.H +
-               ((int64_t)o->h * o->nitems + o->it) * (int64_t)o->len;
-  o->ck_base = a.plan.ck_prefix[o->seq] * a.H + (int64_t)o->h * vjp_ck_count(o->len);
-  o->item_linear = (int64_t)a.plan.item_prefix[o->seq] * a.H + (int64_t)o->h * o->nitems + o->it;
-  return true;
-}
-
 __device__ __forceinline__ void merge_stats(float& m, float& z, float& e, float m2, float z2,
                                             float e2) {
   if (m2 == -CUDART_INF_F) return;
