@@ -796,9 +796,15 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_kernel(VjpArgs a) {
 // tile in shared memory and are never looked at).  The 271-column window is covered by the
 // chunks [0,128), [128,256) and [144,272); only columns >= 256 of the last chunk are used.
 namespace tcl {
-constexpr int kColGroupBytes = 144;                       // 128-byte core + 16 bytes of skew
-constexpr int kRowGroupBytes = (kWinCols / 8) * kColGroupBytes;
-constexpr int kTileBytes = (kVjpRows / 8) * kRowGroupBytes;
+// Core matrices are ordered [column group][row group]: the two row groups of a column group
+// sit 144 bytes apart (128-byte core + 16 bytes of skew against bank conflicts) and column
+// groups 288 bytes apart.  Keeping the row groups close matters for the row-sum MMA, which
+// runs with M = 128 although only 16 rows exist: its 14 surplus row groups then alias the
+// bytes of the following column groups (finite garbage in accumulator rows nobody reads)
+// instead of reaching far beyond the tile.
+constexpr int kRowGroupBytes = 144;
+constexpr int kColGroupBytes = (kVjpRows / 8) * kRowGroupBytes;
+constexpr int kTileBytes = (kWinCols / 8) * kColGroupBytes;
 __host__ __device__ constexpr int chunk_start(int ch) { return ch == 0 ? 0 : ch == 1 ? 128 : kWinCols - 128; }
 static_assert(kVjpRows == 16, "one MMA k-step spans exactly the 16 rows of a block");
 __device__ __forceinline__ int tile_off(int r, int c) {
@@ -814,6 +820,19 @@ __device__ __forceinline__ void store_split(unsigned char* hi, unsigned char* lo
   const __nv_bfloat16 l = __float2bfloat16_rn(v - __bfloat162float(h));
   *reinterpret_cast<__nv_bfloat16*>(hi + off) = h;
   *reinterpret_cast<__nv_bfloat16*>(lo + off) = l;
+}
+// three-term split: v = hi + lo + lo2 to 24 mantissa bits.  The row sums dQz = C kz add
+// thousands of terms that largely cancel (the logit adjoints of a row sum to zero), so their
+// operand keeps full float32 precision; the column sums use the first two terms.
+__device__ __forceinline__ void store_split3(unsigned char* hi, unsigned char* lo,
+                                             unsigned char* lo2, int off, float v) {
+  const __nv_bfloat16 h = __float2bfloat16_rn(v);
+  const float r1 = v - __bfloat162float(h);
+  const __nv_bfloat16 l = __float2bfloat16_rn(r1);
+  const __nv_bfloat16 l2 = __float2bfloat16_rn(r1 - __bfloat162float(l));
+  *reinterpret_cast<__nv_bfloat16*>(hi + off) = h;
+  *reinterpret_cast<__nv_bfloat16*>(lo + off) = l;
+  *reinterpret_cast<__nv_bfloat16*>(lo2 + off) = l2;
 }
 // bytes of the tensor-core operand area: 4 A tiles, qzT, gT hi/lo, kzT, mbarrier + tmem ptr
 __host__ __device__ inline int operand_bytes(int NK, int NV) {
@@ -834,7 +853,7 @@ struct TcSmem {
   static constexpr int kKzSlotBytes = NK * 32;                  // [NK][16] bf16
   static constexpr int kQzBytes = NK * kVjpRows * 2;
   static constexpr int kGBytes = NV * kVjpRows * 2;
-  static constexpr int oQz = 4 * tcl::kTileBytes;               // two buffers
+  static constexpr int oQz = 5 * tcl::kTileBytes;               // two buffers
   static constexpr int oGhi = oQz + 2 * kQzBytes;               // two buffers
   static constexpr int oGlo = oGhi + 2 * kGBytes;               // two buffers
   static constexpr int oKz = oGlo + 2 * kGBytes;
@@ -852,16 +871,18 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   using L = TcSmem<NK, NV>;
   extern __shared__ float4 smem_raw[];
   unsigned char* sbase = reinterpret_cast<unsigned char*>(smem_raw);
-  unsigned char* tChi = sbase;
+  // the three C tiles come first: the row-sum MMA over-reads each of them by 14 row groups
+  // (2 KB), which lands in the tile that follows
+  unsigned char* tChi = sbase;                         // C = hi + lo + lo2 (24 mantissa bits)
   unsigned char* tClo = tChi + tcl::kTileBytes;
-  unsigned char* tPhi = tClo + tcl::kTileBytes;
+  unsigned char* tCl2 = tClo + tcl::kTileBytes;        // third term of C, row sums only
+  unsigned char* tPhi = tCl2 + tcl::kTileBytes;
   unsigned char* tPlo = tPhi + tcl::kTileBytes;
   unsigned char* bKz = sbase + L::oKz;
   uint64_t* mbar = reinterpret_cast<uint64_t*>(sbase + L::oBar);
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(mbar + 1);
   SweepSmem sm = carve_common(reinterpret_cast<float*>(sbase + L::kBytes), NG);
   float* Sbuf = sm.rest;                               // [kVjpRows][kVjpBand] evidence S
-  float* Pbuf = Sbuf + kVjpRows * kVjpBand;            // [kVjpRows][kVjpBand] window product P
 
   Item it;
   if (!load_item_1d(a, &it)) return;
@@ -880,11 +901,13 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   const float4* __restrict__ rowstat = a.rowstat + (int64_t)it.h * a.N + it.start;
   float* ring = ring_slots ? a.ring + it.item_linear * (int64_t)ring_slots * kVjpBand + tid
                            : nullptr;
-  constexpr uint32_t kTmemCols = (5 * NK + 3 * NV) <= 128 ? 128 : 256;
-  constexpr uint32_t kColK = 0, kColV = 3 * NK, kColQ = 3 * NK + 3 * NV, kColQ2 = kColQ + NK;
+  // row-sum k-loop: split over NQ issuing threads, one accumulator each (summed on read-back)
+  constexpr int NQ = NK == 16 ? 4 : 2;
+  constexpr uint32_t kTmemCols = ((3 + NQ) * NK + 3 * NV) <= 128 ? 128 : 256;
+  constexpr uint32_t kColK = 0, kColV = 3 * NK, kColQ = 3 * NK + 3 * NV;
 
   // ---- one-time set-up
-  for (int e = tid; e < 4 * tcl::kTileBytes / 16; e += kVjpBand)
+  for (int e = tid; e < 5 * tcl::kTileBytes / 16; e += kVjpBand)
     reinterpret_cast<uint4*>(tChi)[e] = make_uint4(0, 0, 0, 0);
   if (tid <= D) sm.glut[tid] = expf(neg_md * (float)tid);
   if (warp == 0) tc::tmem_alloc(tmem_ptr, kTmemCols);
@@ -952,14 +975,20 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     }
     if ((mask & 1) && warp == 4) {
       for (int n0 = 0; n0 < NK; n0 += 16) {
-        float v[16], v2[16];
+        float v[16];
         tc::tmem_ld16(tmem + kColQ + n0, v);   // accumulator rows 0..31 = block rows
-        tc::tmem_ld16(tmem + kColQ2 + n0, v2);
+#pragma unroll
+        for (int part = 1; part < NQ; ++part) {
+          float v2[16];
+          tc::tmem_ld16(tmem + kColQ + part * NK + n0, v2);
+#pragma unroll
+          for (int d = 0; d < 16; ++d) v[d] += v2[d];
+        }
         if (lane < b.nrows) {
           float* dst = a.dq_part + (it.rowslot + b.i0 + lane) * D + n0;
 #pragma unroll
           for (int d = 0; d < 16; ++d)
-            if (n0 + d < D) dst[d] = (b.w == it.w_begin) ? v[d] + v2[d] : dst[d] + (v[d] + v2[d]);
+            if (n0 + d < D) dst[d] = (b.w == it.w_begin) ? v[d] : dst[d] + v[d];
         }
       }
     }
@@ -1051,14 +1080,13 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
                                      sm.s_kold[c], jbase + r, sm.glut, kWindowed, W, neg_md);
         has_p |= P != 0.0f;
         Sbuf[r * kVjpBand + tid] = S;
-        if (kWindowed) Pbuf[r * kVjpBand + tid] = P;
       }
       // ---- the previous block's MMAs have had the whole table/forward phase to finish
       if (prev.pending) epilogue(prev);
       // rows of a partial block that do not exist contribute nothing
       for (int r = nrows; r < kVjpRows; ++r) {
         const int off = tcl::tile_off(r, cbase + r);
-        tcl::store_split(tChi, tClo, off, 0.0f);
+        tcl::store_split3(tChi, tClo, tCl2, off, 0.0f);
         tcl::store_split(tPhi, tPlo, off, 0.0f);
       }
       // ---- phase B: adjoint recurrence, rows descending; C and p*d go to the operand tiles
@@ -1092,7 +1120,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
           Sbar = (double)dS + (double)xnext * Sbar;
           const float Cv = act ? Sv * (float)Sbar : 0.0f;
           const int off = tcl::tile_off(r, c);
-          tcl::store_split(tChi, tClo, off, Cv);
+          tcl::store_split3(tChi, tClo, tCl2, off, Cv);
           tcl::store_split(tPhi, tPlo, off, pd);
           xnext = x;
         }
@@ -1101,12 +1129,16 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
           if (slot < 0) slot += ring_slots;
         }
       } else {
+        // The window product is rebuilt from the mismatch-count sum, walked backwards: hs holds
+        // the sum of the window that ends at the current cell (it ended phase A at the last row).
         for (int r = nrows - 1; r >= 0; --r) {
           const bool act = r >= r_first;
-          const int c = cbase + r;
+          const int c = cbase + r, j = jbase + r;
           const float Sv = Sbuf[r * kVjpBand + tid];
-          const float P = Pbuf[r * kVjpBand + tid];
-          const float x = sm.glut[__popc(sm.s_q[r] ^ sm.s_k[c])];
+          const int ham = __popc(sm.s_q[r] ^ sm.s_k[c]);
+          const float P = (act && j >= W) ? __expf(neg_md * (float)hs) : 0.0f;
+          hs += ((act && j > W) ? __popc(sm.s_qold[r] ^ sm.s_kold[c]) : 0) - (act ? ham : 0);
+          const float x = sm.glut[ham];
           float pd;
           const float dS = seed(act, r, c, Sv, &pd);
           float Cv = 0.0f;
@@ -1135,7 +1167,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
             slot = slot == 0 ? ring_slots - 1 : slot - 1;
           }
           const int off = tcl::tile_off(r, c);
-          tcl::store_split(tChi, tClo, off, Cv);
+          tcl::store_split3(tChi, tClo, tCl2, off, Cv);
           tcl::store_split(tPhi, tPlo, off, pd);
         }
       }
@@ -1144,9 +1176,10 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
       tc::fence_before_thread_sync();
       __syncthreads();                                                    // sync 2
       // Four issuing threads (lane 0 of warps 0..3) share the work so that no single warp
-      // falls behind the others at the next barrier: column sums of C, column sums of p*d,
-      // and the two halves of the row-sum k-loop (separate accumulators, added in the
-      // epilogue).  Each issuer commits once; the mbarrier expects four arrivals.
+      // falls behind the others at the next barrier: warp 0 adds the column sums of C, warp 1
+      // those of p*d, and the row-sum k-loop is sliced over the issuers (one accumulator per
+      // slice, added in the epilogue).  Each issuer commits once; the mbarrier expects four
+      // arrivals.
       if (lane == 0 && warp < 4) {
         tc::fence_after_thread_sync();
         constexpr uint32_t idK = tc::idesc_bf16_f32(128, NK, true, false);
@@ -1178,14 +1211,16 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
             if (has_glo) tc::mma_bf16(tmem + kColV + ch * NV, mnPhi + shift, dGlo, idV, true);
           }
         }
-        if (warp >= 2 && (mask & 1)) {
+        if (warp >= 4 - NQ && (mask & 1)) {
           // K-major view (row sums): K direction = column groups, M direction = row groups
           const uint64_t kChi = tc::smem_desc(tc::smem_addr(tChi), tcl::kColGroupBytes, tcl::kRowGroupBytes);
           const uint64_t kClo = tc::smem_desc(tc::smem_addr(tClo), tcl::kColGroupBytes, tcl::kRowGroupBytes);
+          const uint64_t kCl2 = tc::smem_desc(tc::smem_addr(tCl2), tcl::kColGroupBytes, tcl::kRowGroupBytes);
           const uint64_t dKz0 = tc::smem_desc(tc::smem_addr(bKz), NK / 8 * 128, 128);
-          constexpr int kSteps = kWinCols / 16, kHalf = (kSteps + 1) / 2;
-          const int ks0 = warp == 2 ? 0 : kHalf, ks1 = warp == 2 ? kHalf : kSteps;
-          const uint32_t acc = tmem + (warp == 2 ? kColQ : kColQ2);
+          constexpr int kSteps = kWinCols / 16;
+          const int part = warp - (4 - NQ);                       // this issuer's slice of the k-loop
+          const int ks0 = part * kSteps / NQ, ks1 = (part + 1) * kSteps / NQ;
+          const uint32_t acc = tmem + kColQ + part * NK;
           const int g0 = (jwin + (1 << 20)) >> 4;
           int sl = (g0 + ks0) % L::kKzSlots;
 #pragma unroll 1
@@ -1194,6 +1229,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
             const uint64_t shift = (uint64_t)((ks * 2 * tcl::kColGroupBytes) >> 4);
             tc::mma_bf16(acc, kChi + shift, dKz, idQ, ks > ks0);
             tc::mma_bf16(acc, kClo + shift, dKz, idQ, true);
+            tc::mma_bf16(acc, kCl2 + shift, dKz, idQ, true);
             sl = sl + 1 == L::kKzSlots ? 0 : sl + 1;
           }
         }
@@ -1279,11 +1315,7 @@ int launch_sweep2_t(const VjpArgs& a, int items_upper, bool small_dv, cudaStream
 template <int NK, int NV, int NG, bool kWindowed, bool kDropout>
 int launch_sweep2_tc_t(const VjpArgs& a, int items_upper, cudaStream_t stream) {
   size_t bytes = TcSmem<NK, NV>::kBytes +
-                 (sweep_common_floats(NG) + 2 * kVjpRows * kVjpBand) * sizeof(float);
-  // the row-sum MMA reads 16 row groups from the first two tiles: keep that range inside
-  // the allocation
-  const size_t over_read = tcl::kTileBytes + 16 * (size_t)tcl::kRowGroupBytes + 8192;
-  if (bytes < over_read) bytes = over_read;
+                 (sweep_common_floats(NG) + kVjpRows * kVjpBand) * sizeof(float);
   const unsigned grid = (unsigned)((int64_t)items_upper * a.H);
   auto kernel = vjp_sweep2_tc_kernel<NK, NV, NG, kWindowed, kDropout>;
   ROSA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
