@@ -145,56 +145,73 @@ __device__ __forceinline__ bool find_item(const Plan& plan, int slot, int* seq, 
 }
 
 // Dropout counter hash of the operator (reference rosa_soft/soft_reference.py:383-447,
-// rosa_soft/csrc/cuda/rosa_soft_kernels.cu:549-586).
-__device__ __forceinline__ uint32_t avalanche(uint32_t s) {
-  s ^= s >> 16;
+// rosa_soft/csrc/cuda/rosa_soft_kernels.cu:549-586).  One round is
+//   s ^= s >> 16;  s *= 0x7FEB352D;  s ^= s >> 15;  s *= 0x846CA68B;  s ^= s >> 16
+// and the chain is route -> query position -> head -> batch -> seed low -> seed high, each
+// link xor-ing its salted word into the state before the next round.
+//
+// fold16(x) = x ^ (x >> 16) is linear over xor and its own inverse, so the fold that closes one
+// round, the xor of the next word w and the fold that opens the next round collapse into a
+// single xor: fold16(fold16(s) ^ w) = s ^ fold16(w).  The kernels therefore carry the state
+// *open* (before the closing fold), pre-fold the words once, and run only the middle of each
+// round (two multiplies, one shift, two xors) per causal pair.  The first round depends on the
+// route only and is hashed once per key column (dropout_route_open).  The keep test
+// `float(st >> 8) * 2^-24 >= p` is evaluated exactly on integers: the 24-bit value and the
+// power-of-two scaling are exact in float32, so it equals `(st >> 8) >= ceil(p * 2^24)`, i.e.
+// `st >= ceil(p * 2^24) << 8` (the threshold is below 2^24 for every float32 p < 1).
+constexpr uint32_t kQuerySalt = 0xB5297A4Du;
+
+__device__ __forceinline__ uint32_t fold16(uint32_t s) { return s ^ (s >> 16); }
+
+__device__ __forceinline__ uint32_t round_core(uint32_t s) {
   s *= 0x7FEB352Du;
   s ^= s >> 15;
   s *= 0x846CA68Bu;
-  s ^= s >> 16;
   return s;
 }
 
-// The chain is route -> query position -> head -> batch -> seed low -> seed high.  The
-// first round depends on the route only, so callers hash it once per key column
-// (dropout_route_hash) and finish the chain per cell (dropout_keep_from_route).  The keep test
-// `float(st >> 8) * 2^-24 >= p` is evaluated exactly on integers: the 24-bit value and the
-// power-of-two scaling are exact in float32, so it equals `(st >> 8) >= ceil(p * 2^24)`.
 struct DropoutKey {
-  uint32_t head_salted;   // head ^ salt
-  uint32_t batch_salted;  // batch ^ salt
-  uint32_t seed_lo;
-  uint32_t seed_hi_salted;
-  uint32_t threshold;     // ceil(float32(p) * 2^24)
+  uint32_t head_word;   // fold16(head ^ salt)
+  uint32_t batch_word;  // fold16(batch ^ salt)
+  uint32_t seed_lo_word;
+  uint32_t seed_hi_word;
+  uint32_t threshold;   // ceil(float32(p) * 2^24) << 8
 };
 
-__device__ __forceinline__ uint32_t dropout_route_hash(uint32_t route) {
-  return avalanche(route ^ 0x68E31DA4u);
+// Open state of the route round (its closing fold is absorbed by the query round).
+__device__ __forceinline__ uint32_t dropout_route_open(uint32_t route) {
+  return round_core(fold16(route ^ 0x68E31DA4u));
 }
 
-__device__ __forceinline__ bool dropout_keep_from_route(const DropoutKey& k, uint32_t route_hash,
-                                                        uint32_t query) {
-  uint32_t st = avalanche(route_hash ^ query ^ 0xB5297A4Du);
-  st = avalanche(st ^ k.head_salted);
-  st = avalanche(st ^ k.batch_salted);
-  st = avalanche(st ^ k.seed_lo);
-  st = avalanche(st ^ k.seed_hi_salted);
-  return (st >> 8) >= k.threshold;
+// Pre-folded query word.  For a query position i0 + r with i0 a multiple of 2^k and r < 2^k
+// <= 2^16 it equals dropout_query_word(i0) ^ r.
+__device__ __forceinline__ uint32_t dropout_query_word(uint32_t query) {
+  return fold16(query ^ kQuerySalt);
+}
+
+__device__ __forceinline__ bool dropout_keep_open(const DropoutKey& k, uint32_t route_open,
+                                                  uint32_t query_word) {
+  uint32_t st = round_core(route_open ^ query_word);
+  st = round_core(st ^ k.head_word);
+  st = round_core(st ^ k.batch_word);
+  st = round_core(st ^ k.seed_lo_word);
+  st = round_core(st ^ k.seed_hi_word);
+  return fold16(st) >= k.threshold;
 }
 
 __device__ __forceinline__ bool dropout_keep(const DropoutKey& k, uint32_t route, uint32_t query) {
-  return dropout_keep_from_route(k, dropout_route_hash(route), query);
+  return dropout_keep_open(k, dropout_route_open(route), dropout_query_word(query));
 }
 
 __device__ __forceinline__ DropoutKey make_dropout_key(uint32_t head, uint32_t batch,
                                                        const int64_t* seed_ptr, float p) {
   DropoutKey k;
   const uint64_t seed = seed_ptr ? (uint64_t)(*seed_ptr) : 0ull;
-  k.head_salted = head ^ 0x63D83595u;
-  k.batch_salted = batch ^ 0xA511E9B3u;
-  k.seed_lo = (uint32_t)(seed & 0xFFFFFFFFull);
-  k.seed_hi_salted = (uint32_t)(seed >> 32) ^ 0x9E3779B9u;
-  k.threshold = (uint32_t)ceil((double)p * 16777216.0);
+  k.head_word = fold16(head ^ 0x63D83595u);
+  k.batch_word = fold16(batch ^ 0xA511E9B3u);
+  k.seed_lo_word = fold16((uint32_t)(seed & 0xFFFFFFFFull));
+  k.seed_hi_word = fold16((uint32_t)(seed >> 32) ^ 0x9E3779B9u);
+  k.threshold = (uint32_t)ceil((double)p * 16777216.0) << 8;
   return k;
 }
 

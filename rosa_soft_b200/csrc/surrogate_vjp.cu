@@ -223,7 +223,7 @@ __device__ __forceinline__ void fill_block_windows(const SweepSmem& sm, const It
     const int jo = j - W - 1;
     sm.s_kold[c] = (windowed && jo >= 0 && jo < it.len) ? __ldg(k + jo) : 0;
     if (kSmallDv) sm.s_vb[c] = in ? __ldg(vb + j + 1) : 0u;
-    if (want_hash) sm.s_h1[c] = dropout_route_hash((uint32_t)(j + 1));
+    if (want_hash) sm.s_h1[c] = dropout_route_open((uint32_t)(j + 1));
   }
 }
 
@@ -314,8 +314,8 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
   if (tid <= a.D) sm.glut[tid] = expf(neg_md * (float)tid);
 
   // one cell of the forward sweep: returns (e, e * d * u) and, with dropout, the keep flag
-  auto cell = [&](bool act, int r, int c, int j, int i, float& S, int& hs, float& e, float& edu,
-                  bool& keep) {
+  auto cell = [&](bool act, int r, int c, int j, int i, uint32_t qword, float& S, int& hs,
+                  float& e, float& edu, bool& keep) {
     forward_cell(S, hs, act, sm.s_q[r], sm.s_k[c], sm.s_qold[r], sm.s_kold[c], j, sm.glut,
                  windowed, W, neg_md);
     // the log i term cancels in the softmax, so the fixed reference drops it too
@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
     }
     keep = true;
     if (kDropout) {
-      keep = act && dropout_keep_from_route(dkey, sm.s_h1[c], (uint32_t)i);
+      keep = act && dropout_keep_open(dkey, sm.s_h1[c], qword);
       du = keep ? du * inv_keep : 0.0f;
     }
     edu = e * du;
@@ -367,6 +367,7 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
       const int cbase = kVjpBand - 1 - tid;   // column window index on block row 0
       const int jbase = i0 - delta;           // key column on block row 0
       const int vslot = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+      const uint32_t qword0 = dropout_query_word((uint32_t)i0);
 
       if (kFixedRef && nrows == kVjpRows) {
         // full block: four rows per transposing reduction, no tail handling
@@ -377,8 +378,9 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
           for (int rr = 0; rr < 4; ++rr) {
             const int r = r0 + rr;
             bool keep;
-            cell(r >= r_first, r, cbase + r, jbase + r, i0 + r, S, hs, v[2 * rr], v[2 * rr + 1],
-                 keep);
+            // a full block starts on a multiple of kVjpRows, so the row index xors in
+            cell(r >= r_first, r, cbase + r, jbase + r, i0 + r, qword0 ^ (uint32_t)r, S, hs,
+                 v[2 * rr], v[2 * rr + 1], keep);
             if (kDropout) {
               const uint32_t bits = __ballot_sync(0xffffffffu, keep);
               if (lane == 0) keep_out[r * kVjpWarps] = bits;
@@ -398,7 +400,9 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
             const bool in = r0 + rr < nrows;
             bool keep = false;
             float e = 0.0f, edu = 0.0f;
-            if (in) cell(r >= r_first, r, cbase + r, jbase + r, i0 + r, S, hs, e, edu, keep);
+            if (in)
+              cell(r >= r_first, r, cbase + r, jbase + r, i0 + r,
+                   dropout_query_word((uint32_t)(i0 + r)), S, hs, e, edu, keep);
             if (kDropout) {
               const uint32_t bits = __ballot_sync(0xffffffffu, in && keep);
               if (lane == 0 && in) keep_out[r * kVjpWarps] = bits;
@@ -423,7 +427,8 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
                                   : -CUDART_INF_F;
           float du = cell_utility<kSmallDv>(a, it, sm, vb, act, i, j, r, c, ngroups);
           if (use_dropout) {
-            const bool keep = act && dropout_keep_from_route(dkey, sm.s_h1[c], (uint32_t)i);
+            const bool keep =
+                act && dropout_keep_open(dkey, sm.s_h1[c], dropout_query_word((uint32_t)i));
             const uint32_t bits = __ballot_sync(0xffffffffu, keep);
             if (lane == 0) keep_out[r * kVjpWarps] = bits;
             du = keep ? du * inv_keep : 0.0f;
@@ -1184,7 +1189,9 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
         tc::fence_after_thread_sync();
         constexpr uint32_t idK = tc::idesc_bf16_f32(128, NK, true, false);
         constexpr uint32_t idV = tc::idesc_bf16_f32(128, NV, true, false);
-        constexpr uint32_t idQ = tc::idesc_bf16_f32(128, NK, false, false);
+        // the row sums need 16 accumulator rows: M = 64 is the smallest shape and halves the
+        // operand bytes the instruction reads from shared memory (rows 0-15 land in lanes 0-15)
+        constexpr uint32_t idQ = tc::idesc_bf16_f32(64, NK, false, false);
         if (warp == 0 && (mask & 2)) {
           const uint64_t dQz = tc::smem_desc(tc::smem_addr(bQz), NK / 8 * 128, 128);
           // MN-major view (column sums): K direction = row groups, M direction = column groups
