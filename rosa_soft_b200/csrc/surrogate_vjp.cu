@@ -839,11 +839,14 @@ __device__ __forceinline__ void store_split3(unsigned char* hi, unsigned char* l
   *reinterpret_cast<__nv_bfloat16*>(lo + off) = l;
   *reinterpret_cast<__nv_bfloat16*>(lo2 + off) = l2;
 }
-// bytes of the tensor-core operand area: 4 A tiles, qzT, gT hi/lo, kzT, mbarrier + tmem ptr
-__host__ __device__ inline int operand_bytes(int NK, int NV) {
-  return 4 * kTileBytes + NK * kVjpRows * 2 + 2 * NV * kVjpRows * 2 + NK * kWinCols * 2 + 16;
-}
 }  // namespace tcl
+
+// floats of one set of block tables of the tensor-core kernel: the common tables, the block's
+// grad_output rows as float [kVjpRows][NV] and its checkpoints as int2 [kVjpBand]
+__host__ __device__ constexpr int tc_table_floats(int ngroups, int NV) {
+  return 4 * kVjpRows + 4 * kVjpRows * kVjpWarps + kVjpRows * ngroups * 16 + 64 + 2 * kVjpRows +
+         4 * kWinCols + kVjpRows * NV + 2 * kVjpBand;
+}
 
 // geometry of one row block, kept in registers for the deferred epilogue
 struct TcBlock {
@@ -886,8 +889,10 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   unsigned char* bKz = sbase + L::oKz;
   uint64_t* mbar = reinterpret_cast<uint64_t*>(sbase + L::oBar);
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(mbar + 1);
-  SweepSmem sm = carve_common(reinterpret_cast<float*>(sbase + L::kBytes), NG);
-  float* Sbuf = sm.rest;                               // [kVjpRows][kVjpBand] evidence S
+  // two sets of block tables (the set of block b+1 is filled while block b computes), then S
+  float* tab_base = reinterpret_cast<float*>(sbase + L::kBytes);
+  constexpr int kTabFloats = tc_table_floats(NG, NV);
+  float* Sbuf = tab_base + 2 * kTabFloats;             // [kVjpRows][kVjpBand] evidence S
 
   Item it;
   if (!load_item_1d(a, &it)) return;
@@ -914,7 +919,11 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   // ---- one-time set-up
   for (int e = tid; e < 5 * tcl::kTileBytes / 16; e += kVjpBand)
     reinterpret_cast<uint4*>(tChi)[e] = make_uint4(0, 0, 0, 0);
-  if (tid <= D) sm.glut[tid] = expf(neg_md * (float)tid);
+  if (tid <= D) {
+    const float gate = expf(neg_md * (float)tid);
+    carve_common(tab_base, NG).glut[tid] = gate;
+    carve_common(tab_base + kTabFloats, NG).glut[tid] = gate;
+  }
   if (warp == 0) tc::tmem_alloc(tmem_ptr, kTmemCols);
   if (tid == 0) tc::mbar_init(mbar, 4);   // four issuing threads commit per block
   tc::fence_before_thread_sync();
@@ -1000,256 +1009,383 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     tc::fence_before_thread_sync();
   };
 
-  for (int w = it.w_begin; w < it.w_end; ++w) {
-    const int dmin = 1 + w * kVjpBand;
-    const int dmax = dmin + kVjpBand - 1;
-    const int delta = dmin + tid;
-    const bool valid = delta <= it.len - 1;
-    const int rb_lo = dmin / kVjpRows, rb_hi = (it.len - 1) / kVjpRows;
-    const int64_t ck_band = it.ck_base + vjp_ck_before(it.len, w);
-    double Sbar = 0.0, Y = 0.0;
-    float xnext = 0.0f;
-    int live = 0;
-    bool ring_dirty = false;
-    int slot = (valid && ring_slots) ? (it.len - 1 - delta) % ring_slots : 0;
+  // ---- the blocks of this CTA as one flat sequence: bands ascending, row blocks descending
+  struct Geom {
+    int w, rb, rb_lo, i0, nrows, jwin, dmin, dmax;
+    int64_t ck_idx;
+  };
+  auto geom_of = [&](int w, int rb) {
+    Geom g;
+    g.w = w;
+    g.rb = rb;
+    g.dmin = 1 + w * kVjpBand;
+    g.dmax = g.dmin + kVjpBand - 1;
+    g.rb_lo = g.dmin / kVjpRows;
+    g.i0 = max(rb * kVjpRows, g.dmin);
+    g.nrows = min(rb * kVjpRows + kVjpRows - 1, it.len - 1) - g.i0 + 1;
+    g.jwin = rb * kVjpRows - g.dmax;             // window start, a multiple of 16
+    g.ck_idx = it.ck_base + vjp_ck_before(it.len, w) + (rb - g.rb_lo);
+    return g;
+  };
+  const int rb_top = (it.len - 1) / kVjpRows;    // bottom row block of every band
+  auto go_value = [&](const Geom& g, int e) {
+    const int r = e / NV, d = e - r * NV;
+    return (d < Dv && r < g.nrows)
+               ? load_as_float(a.go, (((int64_t)it.start + g.i0 + r) * a.H + it.h) * Dv + d, a.dtype)
+               : 0.0f;
+  };
+  // straight global -> shared fill of one table set (first block of a band)
+  auto fill_direct = [&](const Geom& g, const SweepSmem& t) {
+    fill_block_windows<true>(t, it, q, k, vb, g.i0, g.nrows, g.jwin, kWinCols, kWindowed, W, false);
+    if (tid < g.nrows) t.rstat[tid] = rowstat[g.i0 + tid];
+    if (kDropout && tid < g.nrows * kVjpWarps)
+      t.s_keep[tid] = a.keepbits[(g.ck_idx * kVjpRows) * kVjpWarps + tid];
+    for (int e = tid; e < kVjpRows * NV; e += kVjpBand) t.rest[e] = go_value(g, e);
+    reinterpret_cast<int2*>(t.rest + kVjpRows * NV)[tid] = a.ckpt[g.ck_idx * kVjpBand + tid];
+  };
 
-    for (int rb = rb_hi; rb >= rb_lo; --rb) {
-      const int i0 = max(rb * kVjpRows, dmin), i1 = min(rb * kVjpRows + kVjpRows - 1, it.len - 1);
-      const int nrows = i1 - i0 + 1;
-      const int skew = i0 - rb * kVjpRows;       // 1 on the top block of a band, else 0
-      const int jwin = rb * kVjpRows - dmax;     // window start, a multiple of 16
-      const int ncols = nrows + kVjpBand - 1 + skew;
-      const int64_t ck_idx = ck_band + (rb - rb_lo);
-      unsigned char* bQz = sbase + L::oQz + buf * L::kQzBytes;
-      unsigned char* bGhi = sbase + L::oGhi + buf * L::kGBytes;
-      unsigned char* bGlo = sbase + L::oGlo + buf * L::kGBytes;
+  Geom g = geom_of(it.w_begin, rb_top);
+  int tb = 0;                                    // table set of the block being computed
+  fill_direct(g, carve_common(tab_base, NG));
+  __syncthreads();
+
+  // per-band state of this thread's diagonal
+  int delta = 0, live = 0, slot = 0;
+  bool valid = false, ring_dirty = false, band_start = true;
+  double Sbar = 0.0, Y = 0.0;
+  float xnext = 0.0f;
+
+  while (true) {
+    const SweepSmem sm = carve_common(tab_base + tb * kTabFloats, NG);
+    const SweepSmem nx = carve_common(tab_base + (tb ^ 1) * kTabFloats, NG);
+    const float* s_go = sm.rest;                                     // [kVjpRows][NV]
+    const int2* s_ck = reinterpret_cast<const int2*>(sm.rest + kVjpRows * NV);
+    const int w = g.w, rb = g.rb, i0 = g.i0, nrows = g.nrows, jwin = g.jwin;
+    const int dmin = g.dmin, dmax = g.dmax;
+    const int skew = i0 - rb * kVjpRows;         // 1 on the top block of a band, else 0
+    if (band_start) {
+      delta = dmin + tid;
+      valid = delta <= it.len - 1;
+      Sbar = 0.0;
+      Y = 0.0;
+      xnext = 0.0f;
+      live = 0;
+      ring_dirty = false;
+      slot = (valid && ring_slots) ? (it.len - 1 - delta) % ring_slots : 0;
       // the bottom block of a band refills the whole kz^T ring: the last block of the
       // previous band must have released it
-      if (rb == rb_hi && prev.pending) {
+      if (prev.pending) {
         epilogue(prev);
         prev.pending = false;
       }
-      // (sync 2 of the previous block already separates its phase B from these writes)
-      // ---- block tables
-      fill_block_windows<true>(sm, it, q, k, vb, i0, nrows, jwin, ncols, kWindowed, W, false);
-      if (tid < nrows) sm.rstat[tid] = rowstat[i0 + tid];
-      if (kDropout && tid < nrows * kVjpWarps)
-        sm.s_keep[tid] = a.keepbits[(ck_idx * kVjpRows) * kVjpWarps + tid];
-      build_ulut(a, it, i0, nrows, NG, sm.ulut);
-      const int2 ck = a.ckpt[ck_idx * kVjpBand + tid];
-      __syncthreads();                                                    // sync 1
-      // B operands of the block
-      if (mask & 2)
-        for (int e = tid; e < NK * kVjpRows; e += kVjpBand) {
-          const int d = e / kVjpRows, r = e - d * kVjpRows;
-          const float v = (d < D && r < nrows) ? ((sm.s_q[r] >> d & 1) ? 1.0f : -1.0f) : 0.0f;
-          *reinterpret_cast<__nv_bfloat16*>(bQz + tcl::b_off(d, r, NK)) = __float2bfloat16_rn(v);
-        }
-      if (mask & 4)
-        for (int e = tid; e < NV * kVjpRows; e += kVjpBand) {
-          const int d = e / kVjpRows, r = e - d * kVjpRows;
-          const float g = (d < Dv && r < nrows)
-                              ? load_as_float(a.go, (((int64_t)it.start + i0 + r) * a.H + it.h) * Dv + d,
-                                              a.dtype)
-                              : 0.0f;
-          tcl::store_split(bGhi, bGlo, tcl::b_off(d, r, NV), g);
-        }
-      if (mask & 1) {
-        // kz^T ring: the bottom block of a band fills every k-step, later blocks only the
-        // one key-column group that entered the window
-        const int g0 = (jwin + (1 << 20)) >> 4;           // absolute group of window column 0
-        const int nfill = (rb == rb_hi) ? kWinCols / 16 : 1;
-        for (int e = tid; e < nfill * NK * 16; e += kVjpBand) {
-          const int ks = e / (NK * 16), rem = e - ks * (NK * 16);
-          const int d = rem >> 4, cc = rem & 15;
-          const int c = ks * 16 + cc;
-          const int j = jwin + c;
-          const float v = (d < D && j >= 0 && j < it.len - 1)
-                              ? ((sm.s_k[c] >> d & 1) ? 1.0f : -1.0f)
-                              : 0.0f;
-          const int sl = (g0 + ks) % L::kKzSlots;
-          *reinterpret_cast<__nv_bfloat16*>(bKz + sl * L::kKzSlotBytes + tcl::b_off(d, cc, NK)) =
-              __float2bfloat16_rn(v);
-        }
-      }
-      // ---- phase A: forward recurrence of the block from its checkpoint
-      float S = __int_as_float(ck.x);
-      int hs = ck.y;
-      const int r_first = valid ? max(0, delta - i0) : nrows;
-      const int cbase = kVjpBand - 1 - tid + skew, jbase = i0 - delta;
-      bool has_p = false;
-#pragma unroll 4
-      for (int r = 0; r < nrows; ++r) {
-        const int c = cbase + r;
-        const float P = forward_cell(S, hs, r >= r_first, sm.s_q[r], sm.s_k[c], sm.s_qold[r],
-                                     sm.s_kold[c], jbase + r, sm.glut, kWindowed, W, neg_md);
-        has_p |= P != 0.0f;
-        Sbuf[r * kVjpBand + tid] = S;
-      }
-      // ---- the previous block's MMAs have had the whole table/forward phase to finish
-      if (prev.pending) epilogue(prev);
-      // rows of a partial block that do not exist contribute nothing
-      for (int r = nrows; r < kVjpRows; ++r) {
-        const int off = tcl::tile_off(r, cbase + r);
-        tcl::store_split3(tChi, tClo, tCl2, off, 0.0f);
-        tcl::store_split(tPhi, tPlo, off, 0.0f);
-      }
-      // ---- phase B: adjoint recurrence, rows descending; C and p*d go to the operand tiles
-      const bool warp_p = kWindowed && ring != nullptr && __any_sync(0xffffffffu, has_p);
-      auto seed = [&](bool act, int r, int c, float Sv, float* pd) {
-        const float4 st = sm.rstat[r];
-        const float sq = sqrtf(1.0f + Sv);
-        const float logit = kSqrtScale * (sq - 1.0f) * scale - st.w;
-        const float pr = act ? __expf(logit - st.x) * st.y : 0.0f;
-        float dmul = 1.0f;
-        if (kDropout) dmul = (sm.s_keep[r * kVjpWarps + warp] >> lane & 1u) ? inv_keep : 0.0f;
-        const uint32_t bits = sm.s_vb[c];
-        const float* lut = sm.ulut + r * NG * 16;
-        float u = 0.0f;
-#pragma unroll
-        for (int g = 0; g < NG; ++g) u += lut[g * 16 + ((bits >> (4 * g)) & 15u)];
-        *pd = pr * dmul;
-        const float dlogit = *pd * u - pr * st.z;
-        return scale * dlogit * (0.5f * kSqrtScale) * __frcp_rn(sq);
-      };
-      if (!warp_p && live == 0) {
-        // no window product is alive in this warp: P = 0, T = 0, Y = 0, C = S * Sbar
-#pragma unroll 4
-        for (int r = nrows - 1; r >= 0; --r) {
-          const bool act = r >= r_first;
-          const int c = cbase + r;
-          const float Sv = Sbuf[r * kVjpBand + tid];
-          const float x = sm.glut[__popc(sm.s_q[r] ^ sm.s_k[c])];
-          float pd;
-          const float dS = seed(act, r, c, Sv, &pd);
-          Sbar = (double)dS + (double)xnext * Sbar;
-          const float Cv = act ? Sv * (float)Sbar : 0.0f;
-          const int off = tcl::tile_off(r, c);
-          tcl::store_split3(tChi, tClo, tCl2, off, Cv);
-          tcl::store_split(tPhi, tPlo, off, pd);
-          xnext = x;
-        }
-        if (valid && ring_slots) {
-          slot -= (nrows - r_first) % ring_slots;
-          if (slot < 0) slot += ring_slots;
-        }
-      } else {
-        // The window product is rebuilt from the mismatch-count sum, walked backwards: hs holds
-        // the sum of the window that ends at the current cell (it ended phase A at the last row).
-        for (int r = nrows - 1; r >= 0; --r) {
-          const bool act = r >= r_first;
-          const int c = cbase + r, j = jbase + r;
-          const float Sv = Sbuf[r * kVjpBand + tid];
-          const int ham = __popc(sm.s_q[r] ^ sm.s_k[c]);
-          const float P = (act && j >= W) ? __expf(neg_md * (float)hs) : 0.0f;
-          hs += ((act && j > W) ? __popc(sm.s_qold[r] ^ sm.s_kold[c]) : 0) - (act ? ham : 0);
-          const float x = sm.glut[ham];
-          float pd;
-          const float dS = seed(act, r, c, Sv, &pd);
-          float Cv = 0.0f;
-          double T = 0.0;
-          if (act) {
-            Sbar = (double)dS + (double)xnext * Sbar;
-            T = Sbar * (double)P;
-          }
-          const bool any_p = __any_sync(0xffffffffu, P != 0.0f);
-          if (any_p) {
-            live = W + 2;
-            ring_dirty = true;
-          }
-          if (live > 0) {
-            if (act) {
-              const float tf = (float)T;
-              const float old = ring[(int64_t)slot * kVjpBand];
-              ring[(int64_t)slot * kVjpBand] = tf;
-              Y += (double)tf - (double)old;
-            }
-            if (--live == 0) Y = 0.0;
-          }
-          if (act) {
-            Cv = (float)((double)(Sv + P) * Sbar - Y);
-            xnext = x;
-            slot = slot == 0 ? ring_slots - 1 : slot - 1;
-          }
-          const int off = tcl::tile_off(r, c);
-          tcl::store_split3(tChi, tClo, tCl2, off, Cv);
-          tcl::store_split(tPhi, tPlo, off, pd);
-        }
-      }
-      // ---- phase C: hand the tiles to the tensor core
-      tc::fence_proxy_async_smem();
-      tc::fence_before_thread_sync();
-      __syncthreads();                                                    // sync 2
-      // Four issuing threads (lane 0 of warps 0..3) share the work so that no single warp
-      // falls behind the others at the next barrier: warp 0 adds the column sums of C, warp 1
-      // those of p*d, and the row-sum k-loop is sliced over the issuers (one accumulator per
-      // slice, added in the epilogue).  Each issuer commits once; the mbarrier expects four
-      // arrivals.
-      if (lane == 0 && warp < 4) {
-        tc::fence_after_thread_sync();
-        constexpr uint32_t idK = tc::idesc_bf16_f32(128, NK, true, false);
-        constexpr uint32_t idV = tc::idesc_bf16_f32(128, NV, true, false);
-        // the row sums need 16 accumulator rows: M = 64 is the smallest shape and halves the
-        // operand bytes the instruction reads from shared memory (rows 0-15 land in lanes 0-15)
-        constexpr uint32_t idQ = tc::idesc_bf16_f32(64, NK, false, false);
-        if (warp == 0 && (mask & 2)) {
-          const uint64_t dQz = tc::smem_desc(tc::smem_addr(bQz), NK / 8 * 128, 128);
-          // MN-major view (column sums): K direction = row groups, M direction = column groups
-          const uint64_t mnChi = tc::smem_desc(tc::smem_addr(tChi), tcl::kRowGroupBytes, tcl::kColGroupBytes);
-          const uint64_t mnClo = tc::smem_desc(tc::smem_addr(tClo), tcl::kRowGroupBytes, tcl::kColGroupBytes);
-#pragma unroll
-          for (int ch = 0; ch < 3; ++ch) {
-            // advancing the 14-bit start-address field by whole 16-byte units
-            const uint64_t shift = (uint64_t)(((tcl::chunk_start(ch) >> 3) * tcl::kColGroupBytes) >> 4);
-            tc::mma_bf16(tmem + kColK + ch * NK, mnChi + shift, dQz, idK, false);
-            tc::mma_bf16(tmem + kColK + ch * NK, mnClo + shift, dQz, idK, true);
-          }
-        }
-        if (warp == 1 && (mask & 4)) {
-          const uint64_t dGhi = tc::smem_desc(tc::smem_addr(bGhi), NV / 8 * 128, 128);
-          const uint64_t dGlo = tc::smem_desc(tc::smem_addr(bGlo), NV / 8 * 128, 128);
-          const uint64_t mnPhi = tc::smem_desc(tc::smem_addr(tPhi), tcl::kRowGroupBytes, tcl::kColGroupBytes);
-          const uint64_t mnPlo = tc::smem_desc(tc::smem_addr(tPlo), tcl::kRowGroupBytes, tcl::kColGroupBytes);
-#pragma unroll
-          for (int ch = 0; ch < 3; ++ch) {
-            const uint64_t shift = (uint64_t)(((tcl::chunk_start(ch) >> 3) * tcl::kColGroupBytes) >> 4);
-            tc::mma_bf16(tmem + kColV + ch * NV, mnPhi + shift, dGhi, idV, false);
-            tc::mma_bf16(tmem + kColV + ch * NV, mnPlo + shift, dGhi, idV, true);
-            if (has_glo) tc::mma_bf16(tmem + kColV + ch * NV, mnPhi + shift, dGlo, idV, true);
-          }
-        }
-        if (warp >= 4 - NQ && (mask & 1)) {
-          // K-major view (row sums): K direction = column groups, M direction = row groups
-          const uint64_t kChi = tc::smem_desc(tc::smem_addr(tChi), tcl::kColGroupBytes, tcl::kRowGroupBytes);
-          const uint64_t kClo = tc::smem_desc(tc::smem_addr(tClo), tcl::kColGroupBytes, tcl::kRowGroupBytes);
-          const uint64_t kCl2 = tc::smem_desc(tc::smem_addr(tCl2), tcl::kColGroupBytes, tcl::kRowGroupBytes);
-          const uint64_t dKz0 = tc::smem_desc(tc::smem_addr(bKz), NK / 8 * 128, 128);
-          constexpr int kSteps = kWinCols / 16;
-          const int part = warp - (4 - NQ);                       // this issuer's slice of the k-loop
-          const int ks0 = part * kSteps / NQ, ks1 = (part + 1) * kSteps / NQ;
-          const uint32_t acc = tmem + kColQ + part * NK;
-          const int g0 = (jwin + (1 << 20)) >> 4;
-          int sl = (g0 + ks0) % L::kKzSlots;
-#pragma unroll 1
-          for (int ks = ks0; ks < ks1; ++ks) {
-            const uint64_t dKz = dKz0 + (uint64_t)((sl * L::kKzSlotBytes) >> 4);
-            const uint64_t shift = (uint64_t)((ks * 2 * tcl::kColGroupBytes) >> 4);
-            tc::mma_bf16(acc, kChi + shift, dKz, idQ, ks > ks0);
-            tc::mma_bf16(acc, kClo + shift, dKz, idQ, true);
-            tc::mma_bf16(acc, kCl2 + shift, dKz, idQ, true);
-            sl = sl + 1 == L::kKzSlots ? 0 : sl + 1;
-          }
-        }
-        tc::mma_commit(mbar);
-      }
-      prev.w = w; prev.rb = rb; prev.i0 = i0; prev.nrows = nrows; prev.jwin = jwin;
-      prev.dmin = dmin; prev.dmax = dmax; prev.pending = true;
-      buf ^= 1;
     }
+    // the block after this one
+    const bool next_same = rb > g.rb_lo;
+    const bool has_next = next_same || w + 1 < it.w_end;
+    Geom gn = g;
+    if (has_next) gn = next_same ? geom_of(w, rb - 1) : geom_of(w + 1, rb_top);
+
+    unsigned char* bQz = sbase + L::oQz + buf * L::kQzBytes;
+    unsigned char* bGhi = sbase + L::oGhi + buf * L::kGBytes;
+    unsigned char* bGlo = sbase + L::oGlo + buf * L::kGBytes;
+
+    // ---- prefetch, part 1: the next block of the same band shares all but 16 window columns
+    // with this one; its new columns, rows, row statistics, keep ballots, grad_output rows and
+    // checkpoints are loaded into registers now and stored after the forward phase, so no
+    // global-memory latency is exposed.  One word per thread:
+    //   tid   0-15  key symbol            16-31 key symbol leaving the horizon   32-47 value bits
+    //        48-63  query symbol          64-127 row statistics (16 x float4)    128-255 keep ballots
+    uint32_t pf0 = 0u, pf1 = 0u;
+    constexpr int kGoRegs = (kVjpRows * NV + kVjpBand - 1) / kVjpBand;
+    float pgo[kGoRegs];
+    int2 pck = make_int2(0, 0);
+    if (next_same) {
+      if (tid < 16) {
+        const int j = gn.jwin + tid;
+        pf0 = (j >= 0 && j < it.len - 1) ? (uint32_t)__ldg(k + j) : 0u;
+        const int io = gn.i0 + tid - W - 1;
+        pf1 = (kWindowed && tid < gn.nrows && io >= 0) ? (uint32_t)__ldg(q + io) : 0u;
+      } else if (tid < 32) {
+        const int jo = gn.jwin + (tid - 16) - W - 1;
+        pf0 = (kWindowed && jo >= 0 && jo < it.len) ? (uint32_t)__ldg(k + jo) : 0u;
+      } else if (tid < 48) {
+        const int j = gn.jwin + (tid - 32);
+        pf0 = (j >= 0 && j < it.len - 1) ? __ldg(vb + j + 1) : 0u;
+      } else if (tid < 64) {
+        const int r = tid - 48;
+        pf0 = r < gn.nrows ? (uint32_t)__ldg(q + gn.i0 + r) : 0u;
+      } else if (tid < 128) {
+        const int e = tid - 64;
+        if ((e >> 2) < gn.nrows)
+          pf0 = __float_as_uint(reinterpret_cast<const float*>(rowstat + gn.i0)[e]);
+      } else if (kDropout) {
+        const int e = tid - 128;
+        if (e < gn.nrows * kVjpWarps) pf0 = a.keepbits[(gn.ck_idx * kVjpRows) * kVjpWarps + e];
+      }
+#pragma unroll
+      for (int x = 0; x < kGoRegs; ++x) {
+        const int e = tid + x * kVjpBand;
+        pgo[x] = e < kVjpRows * NV ? go_value(gn, e) : 0.0f;
+      }
+      pck = a.ckpt[gn.ck_idx * kVjpBand + tid];
+    }
+
+    // ---- B operands and utility tables of this block (shared memory only)
+    if (mask & 2)
+      for (int e = tid; e < NK * kVjpRows; e += kVjpBand) {
+        const int d = e / kVjpRows, r = e - d * kVjpRows;
+        const float v = (d < D && r < nrows) ? ((sm.s_q[r] >> d & 1) ? 1.0f : -1.0f) : 0.0f;
+        *reinterpret_cast<__nv_bfloat16*>(bQz + tcl::b_off(d, r, NK)) = __float2bfloat16_rn(v);
+      }
+    if (mask & 4)
+      for (int e = tid; e < NV * kVjpRows; e += kVjpBand) {
+        const int d = e / kVjpRows, r = e - d * kVjpRows;
+        tcl::store_split(bGhi, bGlo, tcl::b_off(d, r, NV), s_go[r * NV + d]);
+      }
+    if (mask & 1) {
+      // kz^T ring: the bottom block of a band fills every k-step, later blocks only the
+      // one key-column group that entered the window
+      const int g0 = (jwin + (1 << 20)) >> 4;           // absolute group of window column 0
+      const int nfill = band_start ? kWinCols / 16 : 1;
+      for (int e = tid; e < nfill * NK * 16; e += kVjpBand) {
+        const int ks = e / (NK * 16), rem = e - ks * (NK * 16);
+        const int d = rem >> 4, cc = rem & 15;
+        const int c = ks * 16 + cc;
+        const int j = jwin + c;
+        const float v = (d < D && j >= 0 && j < it.len - 1)
+                            ? ((sm.s_k[c] >> d & 1) ? 1.0f : -1.0f)
+                            : 0.0f;
+        const int sl = (g0 + ks) % L::kKzSlots;
+        *reinterpret_cast<__nv_bfloat16*>(bKz + sl * L::kKzSlotBytes + tcl::b_off(d, cc, NK)) =
+            __float2bfloat16_rn(v);
+      }
+    }
+    // nibble tables ulut[r][g][nib] = sum_b (nib bit b ? +1 : -1) * gO[i0 + r][4 g + b]
+    for (int e = tid; e < nrows * NG * 16; e += kVjpBand) {
+      const int nib = e & 15, rg = e >> 4;
+      const int r = rg / NG, gq = rg - r * NG;
+      const float* gv = s_go + r * NV + 4 * gq;
+      float sum = 0.0f;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) sum += (nib >> b & 1) ? gv[b] : -gv[b];
+      sm.ulut[e] = sum;
+    }
+
+    // ---- phase A: forward recurrence of the block from its checkpoint
+    const int2 ck = s_ck[tid];
+    float S = __int_as_float(ck.x);
+    int hs = ck.y;
+    const int r_first = valid ? max(0, delta - i0) : nrows;
+    const int cbase = kVjpBand - 1 - tid + skew, jbase = i0 - delta;
+    bool has_p = false;
+#pragma unroll 4
+    for (int r = 0; r < nrows; ++r) {
+      const int c = cbase + r;
+      const float P = forward_cell(S, hs, r >= r_first, sm.s_q[r], sm.s_k[c], sm.s_qold[r],
+                                   sm.s_kold[c], jbase + r, sm.glut, kWindowed, W, neg_md);
+      has_p |= P != 0.0f;
+      Sbuf[r * kVjpBand + tid] = S;
+    }
+
+    // ---- prefetch, part 2: build the next block's tables in the other set
+    if (next_same) {
+      const int c = tid + 16;                    // the 256 window columns both blocks share
+      nx.s_k[c] = sm.s_k[tid];
+      nx.s_kold[c] = sm.s_kold[tid];
+      nx.s_vb[c] = sm.s_vb[tid];
+      if (tid < 16) {
+        nx.s_k[tid] = (int)pf0;
+        nx.s_qold[tid] = (int)pf1;
+      } else if (tid < 32) {
+        nx.s_kold[tid - 16] = (int)pf0;
+      } else if (tid < 48) {
+        nx.s_vb[tid - 32] = pf0;
+      } else if (tid < 64) {
+        nx.s_q[tid - 48] = (int)pf0;
+      } else if (tid < 128) {
+        reinterpret_cast<uint32_t*>(nx.rstat)[tid - 64] = pf0;
+      } else if (kDropout) {
+        nx.s_keep[tid - 128] = pf0;
+      }
+#pragma unroll
+      for (int x = 0; x < kGoRegs; ++x) {
+        const int e = tid + x * kVjpBand;
+        if (e < kVjpRows * NV) nx.rest[e] = pgo[x];
+      }
+      reinterpret_cast<int2*>(nx.rest + kVjpRows * NV)[tid] = pck;
+    } else if (has_next) {
+      fill_direct(gn, nx);
+    }
+
+    // ---- the previous block's MMAs have had the whole table/forward phase to finish
+    if (prev.pending) epilogue(prev);
+    // rows of a partial block that do not exist contribute nothing
+    for (int r = nrows; r < kVjpRows; ++r) {
+      const int off = tcl::tile_off(r, cbase + r);
+      tcl::store_split3(tChi, tClo, tCl2, off, 0.0f);
+      tcl::store_split(tPhi, tPlo, off, 0.0f);
+    }
+    __syncthreads();                             // sync 1: the utility tables are complete
+
+    // ---- phase B: adjoint recurrence, rows descending; C and p*d go to the operand tiles
+    const bool warp_p = kWindowed && ring != nullptr && __any_sync(0xffffffffu, has_p);
+    auto seed = [&](bool act, int r, int c, float Sv, float* pd) {
+      const float4 st = sm.rstat[r];
+      const float sq = sqrtf(1.0f + Sv);
+      const float logit = kSqrtScale * (sq - 1.0f) * scale - st.w;
+      const float pr = act ? __expf(logit - st.x) * st.y : 0.0f;
+      float dmul = 1.0f;
+      if (kDropout) dmul = (sm.s_keep[r * kVjpWarps + warp] >> lane & 1u) ? inv_keep : 0.0f;
+      const uint32_t bits = sm.s_vb[c];
+      const float* lut = sm.ulut + r * NG * 16;
+      float u = 0.0f;
+#pragma unroll
+      for (int gq = 0; gq < NG; ++gq) u += lut[gq * 16 + ((bits >> (4 * gq)) & 15u)];
+      *pd = pr * dmul;
+      const float dlogit = *pd * u - pr * st.z;
+      return scale * dlogit * (0.5f * kSqrtScale) * __frcp_rn(sq);
+    };
+    if (!warp_p && live == 0) {
+      // no window product is alive in this warp: P = 0, T = 0, Y = 0, C = S * Sbar
+#pragma unroll 4
+      for (int r = nrows - 1; r >= 0; --r) {
+        const bool act = r >= r_first;
+        const int c = cbase + r;
+        const float Sv = Sbuf[r * kVjpBand + tid];
+        const float x = sm.glut[__popc(sm.s_q[r] ^ sm.s_k[c])];
+        float pd;
+        const float dS = seed(act, r, c, Sv, &pd);
+        Sbar = (double)dS + (double)xnext * Sbar;
+        const float Cv = act ? Sv * (float)Sbar : 0.0f;
+        const int off = tcl::tile_off(r, c);
+        tcl::store_split3(tChi, tClo, tCl2, off, Cv);
+        tcl::store_split(tPhi, tPlo, off, pd);
+        xnext = x;
+      }
+      if (valid && ring_slots) {
+        slot -= (nrows - r_first) % ring_slots;
+        if (slot < 0) slot += ring_slots;
+      }
+    } else {
+      // The window product is rebuilt from the mismatch-count sum, walked backwards: hs holds
+      // the sum of the window that ends at the current cell (it ended phase A at the last row).
+      for (int r = nrows - 1; r >= 0; --r) {
+        const bool act = r >= r_first;
+        const int c = cbase + r, j = jbase + r;
+        const float Sv = Sbuf[r * kVjpBand + tid];
+        const int ham = __popc(sm.s_q[r] ^ sm.s_k[c]);
+        const float P = (act && j >= W) ? __expf(neg_md * (float)hs) : 0.0f;
+        hs += ((act && j > W) ? __popc(sm.s_qold[r] ^ sm.s_kold[c]) : 0) - (act ? ham : 0);
+        const float x = sm.glut[ham];
+        float pd;
+        const float dS = seed(act, r, c, Sv, &pd);
+        float Cv = 0.0f;
+        double T = 0.0;
+        if (act) {
+          Sbar = (double)dS + (double)xnext * Sbar;
+          T = Sbar * (double)P;
+        }
+        const bool any_p = __any_sync(0xffffffffu, P != 0.0f);
+        if (any_p) {
+          live = W + 2;
+          ring_dirty = true;
+        }
+        if (live > 0) {
+          if (act) {
+            const float tf = (float)T;
+            const float old = ring[(int64_t)slot * kVjpBand];
+            ring[(int64_t)slot * kVjpBand] = tf;
+            Y += (double)tf - (double)old;
+          }
+          if (--live == 0) Y = 0.0;
+        }
+        if (act) {
+          Cv = (float)((double)(Sv + P) * Sbar - Y);
+          xnext = x;
+          slot = slot == 0 ? ring_slots - 1 : slot - 1;
+        }
+        const int off = tcl::tile_off(r, c);
+        tcl::store_split3(tChi, tClo, tCl2, off, Cv);
+        tcl::store_split(tPhi, tPlo, off, pd);
+      }
+    }
+    // ---- phase C: hand the tiles to the tensor core
+    tc::fence_proxy_async_smem();
+    tc::fence_before_thread_sync();
+    __syncthreads();                             // sync 2: tiles, B operands, next tables
+    // Four issuing threads (lane 0 of warps 0..3) share the work so that no single warp
+    // falls behind the others at the next barrier: warp 0 adds the column sums of C, warp 1
+    // those of p*d, and the row-sum k-loop is sliced over the issuers (one accumulator per
+    // slice, added in the epilogue).  Each issuer commits once; the mbarrier expects four
+    // arrivals.
+    if (lane == 0 && warp < 4) {
+      tc::fence_after_thread_sync();
+      constexpr uint32_t idK = tc::idesc_bf16_f32(128, NK, true, false);
+      constexpr uint32_t idV = tc::idesc_bf16_f32(128, NV, true, false);
+      // the row sums need 16 accumulator rows: M = 64 is the smallest shape and halves the
+      // operand bytes the instruction reads from shared memory (rows 0-15 land in lanes 0-15)
+      constexpr uint32_t idQ = tc::idesc_bf16_f32(64, NK, false, false);
+      if (warp == 0 && (mask & 2)) {
+        const uint64_t dQz = tc::smem_desc(tc::smem_addr(bQz), NK / 8 * 128, 128);
+        // MN-major view (column sums): K direction = row groups, M direction = column groups
+        const uint64_t mnChi = tc::smem_desc(tc::smem_addr(tChi), tcl::kRowGroupBytes, tcl::kColGroupBytes);
+        const uint64_t mnClo = tc::smem_desc(tc::smem_addr(tClo), tcl::kRowGroupBytes, tcl::kColGroupBytes);
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) {
+          // advancing the 14-bit start-address field by whole 16-byte units
+          const uint64_t shift = (uint64_t)(((tcl::chunk_start(ch) >> 3) * tcl::kColGroupBytes) >> 4);
+          tc::mma_bf16(tmem + kColK + ch * NK, mnChi + shift, dQz, idK, false);
+          tc::mma_bf16(tmem + kColK + ch * NK, mnClo + shift, dQz, idK, true);
+        }
+      }
+      if (warp == 1 && (mask & 4)) {
+        const uint64_t dGhi = tc::smem_desc(tc::smem_addr(bGhi), NV / 8 * 128, 128);
+        const uint64_t dGlo = tc::smem_desc(tc::smem_addr(bGlo), NV / 8 * 128, 128);
+        const uint64_t mnPhi = tc::smem_desc(tc::smem_addr(tPhi), tcl::kRowGroupBytes, tcl::kColGroupBytes);
+        const uint64_t mnPlo = tc::smem_desc(tc::smem_addr(tPlo), tcl::kRowGroupBytes, tcl::kColGroupBytes);
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) {
+          const uint64_t shift = (uint64_t)(((tcl::chunk_start(ch) >> 3) * tcl::kColGroupBytes) >> 4);
+          tc::mma_bf16(tmem + kColV + ch * NV, mnPhi + shift, dGhi, idV, false);
+          tc::mma_bf16(tmem + kColV + ch * NV, mnPlo + shift, dGhi, idV, true);
+          if (has_glo) tc::mma_bf16(tmem + kColV + ch * NV, mnPhi + shift, dGlo, idV, true);
+        }
+      }
+      if (warp >= 4 - NQ && (mask & 1)) {
+        // K-major view (row sums): K direction = column groups, M direction = row groups
+        const uint64_t kChi = tc::smem_desc(tc::smem_addr(tChi), tcl::kColGroupBytes, tcl::kRowGroupBytes);
+        const uint64_t kClo = tc::smem_desc(tc::smem_addr(tClo), tcl::kColGroupBytes, tcl::kRowGroupBytes);
+        const uint64_t kCl2 = tc::smem_desc(tc::smem_addr(tCl2), tcl::kColGroupBytes, tcl::kRowGroupBytes);
+        const uint64_t dKz0 = tc::smem_desc(tc::smem_addr(bKz), NK / 8 * 128, 128);
+        constexpr int kSteps = kWinCols / 16;
+        const int part = warp - (4 - NQ);                       // this issuer's slice of the k-loop
+        const int ks0 = part * kSteps / NQ, ks1 = (part + 1) * kSteps / NQ;
+        const uint32_t acc = tmem + kColQ + part * NK;
+        const int g0 = (jwin + (1 << 20)) >> 4;
+        int sl = (g0 + ks0) % L::kKzSlots;
+#pragma unroll 1
+        for (int ks = ks0; ks < ks1; ++ks) {
+          const uint64_t dKz = dKz0 + (uint64_t)((sl * L::kKzSlotBytes) >> 4);
+          const uint64_t shift = (uint64_t)((ks * 2 * tcl::kColGroupBytes) >> 4);
+          tc::mma_bf16(acc, kChi + shift, dKz, idQ, ks > ks0);
+          tc::mma_bf16(acc, kClo + shift, dKz, idQ, true);
+          tc::mma_bf16(acc, kCl2 + shift, dKz, idQ, true);
+          sl = sl + 1 == L::kKzSlots ? 0 : sl + 1;
+        }
+      }
+      tc::mma_commit(mbar);
+    }
+    prev.w = w; prev.rb = rb; prev.i0 = i0; prev.nrows = nrows; prev.jwin = jwin;
+    prev.dmin = dmin; prev.dmax = dmax; prev.pending = true;
+    buf ^= 1;
     // leave the ring zeroed for the next band of this item
-    if (ring != nullptr && ring_dirty && w + 1 < it.w_end) {
+    if (!next_same && ring != nullptr && ring_dirty && has_next) {
       for (int s = 0; s < ring_slots; ++s) ring[(int64_t)s * kVjpBand] = 0.0f;
     }
+    if (!has_next) break;
+    band_start = !next_same;
+    g = gn;
+    tb ^= 1;
   }
   if (prev.pending) epilogue(prev);
   __syncthreads();
@@ -1322,7 +1458,7 @@ int launch_sweep2_t(const VjpArgs& a, int items_upper, bool small_dv, cudaStream
 template <int NK, int NV, int NG, bool kWindowed, bool kDropout>
 int launch_sweep2_tc_t(const VjpArgs& a, int items_upper, cudaStream_t stream) {
   size_t bytes = TcSmem<NK, NV>::kBytes +
-                 (sweep_common_floats(NG) + kVjpRows * kVjpBand) * sizeof(float);
+                 (2 * tc_table_floats(NG, NV) + kVjpRows * kVjpBand) * sizeof(float);
   const unsigned grid = (unsigned)((int64_t)items_upper * a.H);
   auto kernel = vjp_sweep2_tc_kernel<NK, NV, NG, kWindowed, kDropout>;
   ROSA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
