@@ -50,7 +50,8 @@ enum rosa_b200_status {
   ROSA_B200_STATUS_OK = 0,
   ROSA_B200_STATUS_BAD_FIRST_OFFSET = 1, /* cu_seqlens[0] != 0            */
   ROSA_B200_STATUS_NOT_MONOTONE = 2,     /* cu_seqlens decreases somewhere */
-  ROSA_B200_STATUS_BAD_LAST_OFFSET = 3   /* cu_seqlens[-1] != N            */
+  ROSA_B200_STATUS_BAD_LAST_OFFSET = 3,  /* cu_seqlens[-1] != N            */
+  ROSA_B200_STATUS_CAPACITY = 4          /* a slot would outgrow the history capacity */
 };
 
 ROSA_B200_API int rosa_b200_abi_version(void);
@@ -132,6 +133,39 @@ ROSA_B200_API int rosa_b200_hard_inference(const uint32_t* query_symbols, const 
                              const int32_t* cu_seqlens, int64_t num_seq, int64_t uniform_len,
                              int64_t max_suffix_length, float* out, int64_t* matched_end,
                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------ streaming hard inference
+ * Chunked update with the per-slot state kept on the GPU: the device form of
+ * RosaRuntime::update_packed (reference rosa_soft/csrc/rosa_runtime.cpp:333-482; the
+ * automaton step it replaces :103-133; successor payload :455-467; reset :492-498).
+ * The caller owns the state and passes it to every call:
+ *   key_history     uint8  [slots, num_heads, capacity]          key symbols seen so far
+ *   run_state       uint16 [slots, num_heads, capacity]          capped run length per diagonal
+ *   payload_history uint8  [slots, num_payload_heads, capacity]
+ *   lengths         int32  [slots]                               tokens held per slot
+ * A fresh or reset runtime is `lengths` = 0; the other arrays need no initialisation.
+ * The chunk is token-major: query/key [chunk_tokens, num_heads], payload
+ * [chunk_tokens, num_payload_heads], `chunk_offsets` int32 [slots + 1] on the device
+ * (slot s owns chunk tokens [offsets[s], offsets[s+1]); empty slots allowed).  Symbols are
+ * masked to qk_bits / payload_bits (1..8).  For every chunk token and head the call writes
+ * the payload symbol that followed the latest-longest match (0 for no match) to `output`
+ * and the matched key end position inside the slot's whole history (-1 for no match) to
+ * `matched_key_end`, appends the chunk to the histories and advances `lengths`.
+ * `max_length_after` is a host-side upper bound of lengths[s] + chunk length over the slots
+ * (it sizes the grid; the host knows it because it chose the chunk).  The result does not
+ * depend on how a stream was cut into chunks.  max_suffix_length <= 65535.
+ * A bad `chunk_offsets` or a slot that would outgrow `capacity` leaves the state untouched
+ * and is reported through rosa_b200_read_status (ROSA_B200_STATUS_CAPACITY for the latter).
+ * Calls that share a state must be ordered on one stream. */
+ROSA_B200_API size_t rosa_b200_stream_workspace_bytes(int64_t chunk_tokens, int num_heads);
+
+ROSA_B200_API int rosa_b200_stream_update(
+    const uint8_t* query, const uint8_t* key, const uint8_t* payload,
+    const int32_t* chunk_offsets, int64_t chunk_tokens, int slots, int num_heads,
+    int num_payload_heads, int qk_bits, int payload_bits, int64_t max_suffix_length,
+    uint8_t* key_history, uint16_t* run_state, uint8_t* payload_history, int32_t* lengths,
+    int64_t capacity, int64_t max_length_after, uint8_t* output, int64_t* matched_key_end,
+    void* workspace, size_t workspace_bytes, void* stream);
 
 /* Per-kernel timing for benchmarks (no counterpart in the reference, which times whole
  * steps with CUDA events in benchmarks/rosa_soft.py:151-173).  While enabled, every kernel

@@ -64,16 +64,18 @@ class BuildCapabilities:
 BUILD_CAPABILITIES = BuildCapabilities(
     variant="cuda",
     compiled_extension=True,
-    rosa_runtime=False,
+    rosa_runtime=True,   # the GPU-resident streaming runtime of runtime.py
     rosa_soft_cuda=True,
 )
 
 from .inference import rosa_hard_inference  # noqa: E402
+from .runtime import RosaRuntime  # noqa: E402
 from .soft import rosa_soft, rosa_soft_varlen  # noqa: E402
 
 __all__ = [
     "__version__",
     "BUILD_CAPABILITIES",
+    "RosaRuntime",
     "rosa_hard_inference",
     "rosa_soft",
     "rosa_soft_varlen",

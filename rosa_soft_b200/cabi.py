@@ -24,6 +24,8 @@ EXPORTED_SYMBOLS = (
     "rosa_b200_surrogate_vjp",
     "rosa_b200_hard_inference_workspace_bytes",
     "rosa_b200_hard_inference",
+    "rosa_b200_stream_workspace_bytes",
+    "rosa_b200_stream_update",
     "rosa_b200_read_status",
     "rosa_b200_profile_enable",
     "rosa_b200_profile_collect",
@@ -63,6 +65,11 @@ def load() -> ctypes.CDLL:
     lib.rosa_b200_hard_inference.restype = i32
     lib.rosa_b200_hard_inference.argtypes = [vp, vp, vp, i64, i32, i32, i32, vp, i64, i64, i64, vp,
                                              vp, vp, sz, vp]
+    lib.rosa_b200_stream_workspace_bytes.restype = sz
+    lib.rosa_b200_stream_workspace_bytes.argtypes = [i64, i32]
+    lib.rosa_b200_stream_update.restype = i32
+    lib.rosa_b200_stream_update.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i64, vp,
+                                            vp, vp, vp, i64, i64, vp, vp, vp, sz, vp]
     lib.rosa_b200_read_status.restype = i32
     lib.rosa_b200_read_status.argtypes = [vp, vp, ctypes.POINTER(i32)]
     lib.rosa_b200_profile_enable.restype = None
@@ -215,6 +222,34 @@ def hard_inference(qsym, ksym, payload, cu_seqlens, max_suffix_length, stream=No
     check(lib.rosa_b200_hard_inference(_ptr(qsym), _ptr(ksym), _ptr(payload), N, H, Hp, Dp,
                                        _ptr(cu), S, T, int(max_suffix_length), _ptr(out), _ptr(end),
                                        _ptr(ws), nbytes, ctypes.c_void_p(st)))
+    return out, end, ws
+
+
+def stream_update(query, key, payload, chunk_offsets, qk_bits, payload_bits, max_suffix_length,
+                  key_history, run_state, payload_history, lengths, max_length_after, stream=None):
+    """One chunked update of the GPU streaming runtime.
+
+    query/key uint8 [n, H], payload uint8 [n, Hp], chunk_offsets int32 [slots + 1] (device);
+    state tensors as described in include/rosa_soft_b200.h.  Returns (output uint8 [n, H],
+    matched_key_end int64 [n, H], workspace)."""
+    import torch
+
+    lib = load()
+    n, H = query.shape
+    Hp = payload.shape[1]
+    slots = chunk_offsets.numel() - 1
+    capacity = key_history.shape[-1]
+    out = torch.empty((n, H), dtype=torch.uint8, device=query.device)
+    end = torch.empty((n, H), dtype=torch.int64, device=query.device)
+    nbytes = lib.rosa_b200_stream_workspace_bytes(n, H)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
+    st = stream if stream is not None else torch.cuda.current_stream(query.device).cuda_stream
+    check(lib.rosa_b200_stream_update(_ptr(query), _ptr(key), _ptr(payload), _ptr(chunk_offsets), n,
+                                      slots, H, Hp, int(qk_bits), int(payload_bits),
+                                      int(max_suffix_length), _ptr(key_history), _ptr(run_state),
+                                      _ptr(payload_history), _ptr(lengths), capacity,
+                                      int(max_length_after), _ptr(out), _ptr(end), _ptr(ws), nbytes,
+                                      ctypes.c_void_p(st)))
     return out, end, ws
 
 

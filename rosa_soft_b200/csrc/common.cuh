@@ -285,6 +285,27 @@ int launch_inference_finish(const Plan& plan, const unsigned long long* best, co
 int launch_transpose_symbols(const uint32_t* q, const uint32_t* k, int64_t N, int H, int32_t* qt,
                              int32_t* kt, cudaStream_t stream);
 
+// One chunked update of the streaming runtime (stream_runtime.cu).
+struct StreamArgs {
+  const uint8_t* query;        // [chunk_tokens, H] packed symbols of the chunk
+  const uint8_t* key;          // [chunk_tokens, H]
+  const uint8_t* payload;      // [chunk_tokens, Hp]
+  const int32_t* offsets;      // [slots + 1] chunk offsets per slot
+  int64_t chunk_tokens;
+  int slots, H, Hp, qk_mask, payload_mask, W;
+  uint8_t* key_history;        // [slots, H, capacity]
+  uint16_t* run_state;         // [slots, H, capacity] capped run length per diagonal
+  uint8_t* payload_history;    // [slots, Hp, capacity]
+  int32_t* lengths;            // [slots] tokens held per slot, advanced by the call
+  int64_t capacity;
+  int64_t max_length_after;    // upper bound of lengths[s] + chunk length over the slots
+  uint8_t* output;             // [chunk_tokens, H]
+  int64_t* matched_end;        // [chunk_tokens, H]
+  unsigned long long* best;    // [chunk_tokens, H] scratch
+  int32_t* status;             // 4 words
+};
+int launch_stream_update(const StreamArgs& a, cudaStream_t stream);
+
 struct VjpArgs {
   Plan plan;
   const void* q;

@@ -119,3 +119,40 @@ def test_validation_matrix():
     assert seed.numel() == 0 and seed.dtype == torch.int64
     assert sc.make_dropout_seed(q, 0.5, False).numel() == 0
     assert sc.make_dropout_seed(q, 0.5, True).shape == ()
+
+
+def test_runtime_constructor_and_input_contract_without_a_gpu():
+    """Mirrors the argument errors of the reference runtime (rosa_soft/runtime.py:320-352,
+    165-239); none of them needs a device."""
+    from rosa_soft_b200 import RosaRuntime
+    from rosa_soft_b200.runtime import pack_sign_bits, unpack_sign_bits
+    with pytest.raises(ValueError, match=r"qk_bits must be in \[1, 8\]"):
+        RosaRuntime(4, qk_bits=9)
+    with pytest.raises(ValueError, match=r"payload_bits must be in \[1, 8\]"):
+        RosaRuntime(4, payload_bits=0)
+    with pytest.raises(TypeError, match="num_heads must be an integer"):
+        RosaRuntime(True)
+    with pytest.raises(ValueError, match="divisible"):
+        RosaRuntime(4, 3)
+    rt = RosaRuntime(4, 2, 3, 5, 16)
+    assert (rt.num_heads, rt.num_payload_heads, rt.qk_bits, rt.payload_bits,
+            rt.max_suffix_length, rt.state) == (4, 2, 3, 5, 16, "OPEN")
+    u8 = lambda *shape: torch.zeros(shape, dtype=torch.uint8)
+    with pytest.raises(TypeError, match="dtype torch.uint8"):
+        rt.update_packed(u8(1, 2, 4).int(), u8(1, 2, 4), u8(1, 2, 2))
+    with pytest.raises(ValueError, match="shapes differ"):
+        rt.update_packed(u8(1, 2, 4), u8(1, 3, 4), u8(1, 2, 2))
+    with pytest.raises(ValueError, match=r"\[B, T, H\]"):
+        rt.update_packed(u8(2, 4), u8(2, 4), u8(2, 2))
+    with pytest.raises(ValueError, match="CUDA tensors"):
+        rt.update_packed(u8(1, 2, 4), u8(1, 2, 4), u8(1, 2, 2))
+    with pytest.raises(ValueError, match="last dimension must equal qk_bits"):
+        rt.update(torch.zeros(1, 2, 4, 2), torch.zeros(1, 2, 4, 2), torch.zeros(1, 2, 2, 5))
+    x = torch.tensor([[0.5, -1.0, 0.0, 2.0, float("nan")]])
+    packed = pack_sign_bits(x)
+    assert packed.tolist() == [0b01001]                      # zero and NaN are not positive
+    assert unpack_sign_bits(packed, 5, torch.float32).tolist() == [[1.0, -1.0, -1.0, 1.0, -1.0]]
+    rt.close()
+    rt.close()
+    with pytest.raises(RuntimeError, match="closed"):
+        rt.reset()
