@@ -46,6 +46,10 @@ WORKLOADS = {
     # batched hard inference: 64 streams x 16384 tokens x 64 heads of 32-bit symbols, forward only
     "c5": dict(kind="inference", B=64, T=16384, H=64, D=32, Hv=64, Dv=8, W=32, scale=1.0, p=0.0,
                m=3.0, dtype="float32", gen="symbols"),
+    # streaming runtime: 64 slots x 16384 tokens x 64 heads of 8-bit symbols fed in chunks of 2048
+    # tokens per slot to a runtime whose state stays on the GPU (the reference's RosaRuntime use)
+    "stream": dict(kind="stream", B=64, T=16384, H=64, D=8, Hv=64, Dv=8, W=32, chunk=2048, scale=1.0,
+                   p=0.0, m=3.0, dtype="uint8", gen="symbols"),
     "small": dict(B=1, T=1024, H=8, D=8, Hv=2, Dv=8, W=128, scale=1.0, p=0.1, m=3.0,
                   dtype="bfloat16", gen="randn"),
 }
@@ -169,6 +173,77 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
+def make_stream_inputs(cfg, seed, device):
+    """i.i.d. 8-bit symbols per (slot, head); 10 % of the positions start a copy of an earlier
+    window of 8..512 tokens into both streams, so that matches reach the horizon."""
+    import numpy as np
+    import torch
+
+    rng = np.random.default_rng(seed)
+    B, T, H = cfg["B"], cfg["T"], cfg["H"]
+    hi = 1 << cfg["D"]
+    k = rng.integers(0, hi, size=(B, T, H), dtype=np.uint8)
+    q = rng.integers(0, hi, size=(B, T, H), dtype=np.uint8)
+    for b in range(B):
+        t = 600
+        while t < T - 520:
+            if rng.random() < 0.1:
+                n = int(rng.integers(8, 513))
+                src = int(rng.integers(0, t - n))
+                k[b, t:t + n] = k[b, src:src + n]
+                q[b, t + 1:t + 1 + n] = k[b, src + 1:src + 1 + n]
+                t += n
+            t += int(rng.integers(1, 20))
+    payload = rng.integers(0, 1 << cfg["Dv"], size=(B, T, cfg["Hv"]), dtype=np.uint8)
+    to = lambda a: torch.from_numpy(a).to(device)
+    return to(q), to(k), to(payload)
+
+
+def cpu_stream_run(cfg, steps, warmup):
+    """The reference's own RosaRuntime (suffix automata on the host cores, compiled from its
+    source into oracle/_ref/) fed the same chunks; the oracle's one-shot matcher when that
+    library is absent."""
+    import numpy as np
+    import torch
+
+    sample = dict(cfg, B=16)
+    q, k, pay = make_stream_inputs(sample, 7, "cpu")
+    B, T, H, chunk = sample["B"], sample["T"], sample["H"], sample["chunk"]
+    lib = os.path.join(ROOT, "oracle", "_ref", "librosa_runtime_ref.so")
+    times = []
+    if os.path.exists(lib):
+        torch.classes.load_library(lib)
+        runtime = torch.classes.rosa_soft.RosaRuntime(H, sample["Hv"], sample["D"], sample["Dv"],
+                                                      sample["W"])
+        for it in range(warmup + steps):
+            runtime.reset()
+            t0 = time.perf_counter()
+            for a in range(0, T, chunk):
+                n = min(chunk, T - a)
+                cu = torch.arange(B + 1, dtype=torch.int64) * n
+                flat = lambda x: x[:, a:a + n].reshape(B * n, -1).contiguous()
+                runtime.update_packed(cu, flat(q), flat(k), flat(pay))
+            if it >= warmup:
+                times.append(time.perf_counter() - t0)
+        kind, cores = "reference", torch.get_num_threads()
+        what = "the reference's RosaRuntime (suffix automata, OpenMP over slot x head)"
+    else:
+        from oracle import rosa_oracle as orc
+        cu = np.arange(B + 1, dtype=np.int64) * T
+        flat = lambda x: x.numpy().reshape((B * T,) + tuple(x.shape[2:]))
+        for it in range(warmup + steps):
+            t0 = time.perf_counter()
+            orc.hard_inference(flat(q).astype(np.uint32), flat(k).astype(np.uint32),
+                               flat(pay).astype(np.float32)[:, :, None], cu, sample["W"])
+            if it >= warmup:
+                times.append(time.perf_counter() - t0)
+        kind, cores = "port", orc.num_threads()
+        what = "the oracle's one-shot matcher (reference runtime library not built)"
+    sec = sum(times) / len(times)
+    desc = f"{B} of the {cfg['B']} slots x T={T} x H={H} in chunks of {chunk}: {what}"
+    return B * T * H / sec / 1e6, sec, cores, desc, kind
+
+
 def cpu_reference_run(cfg, steps, warmup):
     """Times the oracle (CPU restatement of the reference algorithm) on a bounded sample."""
     import numpy as np
@@ -227,7 +302,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    config = {"workload": f"{args.workload}: rosa_soft fwd+bwd, per rank B={cfg['B']} T={cfg['T']} "
+    what = {"inference": "batched hard inference, forward only",
+            "stream": f"RosaRuntime chunked updates ({cfg.get('chunk')} tokens per slot and call), "
+                      "forward only",
+            "varlen": "rosa_soft_varlen fwd+bwd"}.get(cfg.get("kind"), "rosa_soft fwd+bwd")
+    config = {"workload": f"{args.workload}: {what}, per rank B={cfg['B']} T={cfg['T']} "
                           f"H={cfg['H']} D={cfg['D']} Hv={cfg['Hv']} Dv={cfg['Dv']} W={cfg['W']} "
                           f"p={cfg['p']} m={cfg['m']} scale={cfg['scale']} {cfg['dtype']}",
               "global_batch": cfg["B"] * world, "seq_len": cfg["T"],
@@ -238,15 +317,25 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        value, sec, cores, desc = cpu_reference_run(cfg, max(1, args.steps), max(0, min(args.warmup, 1)))
+        base_kind = "port"
+        if cfg.get("kind") == "stream":
+            value, sec, cores, desc, base_kind = cpu_stream_run(cfg, max(1, args.steps),
+                                                                max(0, min(args.warmup, 1)))
+        else:
+            value, sec, cores, desc = cpu_reference_run(cfg, max(1, args.steps),
+                                                        max(0, min(args.warmup, 1)))
+        forward_only = cfg.get("kind") in ("inference", "stream")
         print(json.dumps({
-            "impl": "reference", "metric": "fwd+bwd M token-heads/s", "value": value,
+            "impl": "reference",
+            "metric": "forward M token-heads/s" if forward_only else "fwd+bwd M token-heads/s",
+            "value": value,
             "unit": "M token-heads/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "u8 symbols" if cfg.get("kind") == "stream" else "f64", "data": "synthetic",
             "config": config,
             "cpu_baseline": {"value": value, "unit": "M token-heads/s", "cores": cores,
-                             "kind": "port", "sample": desc},
+                             "kind": base_kind, "sample": desc},
             "e2e": {"value": value, "unit": "M token-heads/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0},
         }))
@@ -266,6 +355,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     dtype = getattr(torch, cfg["dtype"])
     kind = cfg.get("kind", "dense")
+    forward_only = kind in ("inference", "stream")
     kw = dict(max_suffix_length=cfg["W"], scale=cfg["scale"], dropout_p=cfg["p"], mismatch_scale=cfg["m"])
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
     if kind == "inference":
@@ -274,6 +364,20 @@ def main():
 
         def step(qs, ks, pay):
             return list(rs.rosa_hard_inference(qs, ks, pay, max_suffix_length=cfg["W"]))
+    elif kind == "stream":
+        inputs = list(make_stream_inputs(cfg, 1000 + rank, dev))
+        pairs = cfg["B"] * cfg["H"] * cfg["T"] * (cfg["T"] - 1) // 2
+        runtime = rs.RosaRuntime(cfg["H"], cfg["Hv"], cfg["D"], cfg["Dv"], cfg["W"])
+
+        def step(qs, ks, pay):
+            runtime.reset()
+            outs, ends = [], []
+            for a in range(0, cfg["T"], cfg["chunk"]):
+                b = min(cfg["T"], a + cfg["chunk"])
+                out, end = runtime.update_packed(qs[:, a:b], ks[:, a:b], pay[:, a:b])
+                outs.append(out)
+                ends.append(end)
+            return [torch.cat(outs, dim=1), torch.cat(ends, dim=1)]
     elif kind == "varlen":
         lengths = varlen_lengths(cfg, 1004)
         cu = torch.tensor([0] + list(__import__("itertools").accumulate(lengths)), dtype=torch.int32,
@@ -366,7 +470,7 @@ def main():
     except OSError:
         pass
     flop = (6 * cfg["D"] + 4 * cfg["Dv"]) * pairs           # algorithmic contraction FLOP per launch
-    if kind == "inference":
+    if forward_only:
         flop = 0
     k_ms, k_n = kernels.get("vjp_sweep2", (0.0, 0))
     k_avg_s = (k_ms / k_n / 1e3) if k_n else None
@@ -376,20 +480,26 @@ def main():
         tensor_peak, peak_note = 1400.0, "fallback"
     achieved = flop / k_avg_s / 1e12 if k_avg_s else None
     s = 2 if cfg["dtype"] != "float32" else 4
-    per_unit = (80 if kind == "inference" else
+    per_unit = (80 if kind == "inference" else 12 if kind == "stream" else
                 2 * cfg["D"] * s + cfg["Dv"] * s * cfg["Hv"] / cfg["H"] + cfg["Dv"] * s + 8)
     fwd_bytes = per_unit * cfg["B"] * cfg["T"] * cfg["H"]
     fwd_ms = sum(kernels.get(n, (0.0, 0))[0] for n in ("pack_symbols", "transpose_symbols", "hard_match",
-                                                       "gather_output", "inference_finish"))
-    fwd_n = kernels.get("hard_match", (0.0, 1))[1] or 1
+                                                       "gather_output", "inference_finish",
+                                                       "stream_prepare", "stream_append", "stream_match",
+                                                       "stream_finish"))
+    fwd_n = 1 if kind == "stream" else (kernels.get("hard_match", (0.0, 1))[1] or 1)
+    if kind == "stream":
+        fwd_ms /= args.steps
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
     fwd_gbs = fwd_bytes / (fwd_ms / fwd_n / 1e3) / 1e9 if fwd_ms else None
     result = {
-        "metric": ("forward M token-heads/s" if kind == "inference" else "fwd+bwd M token-heads/s"),
+        "metric": ("forward M token-heads/s" if forward_only else "fwd+bwd M token-heads/s"),
         "value": units * args.steps / (total_ms / 1e3) / 1e6,
         "unit": "M token-heads/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32 accumulate on " + cfg["dtype"] + " inputs; integer symbols",
+        "vs_baseline": None,
+        "dtype": ("u8 symbols" if kind == "stream" else
+                  "f32 accumulate on " + cfg["dtype"] + " inputs; integer symbols"),
         "data": "synthetic", "config": config,
         "clocks": clocks.summary(),
         "e2e": {"value": units * args.steps / (e2e_ms / 1e3) / 1e6, "unit": "M token-heads/s",
@@ -407,15 +517,21 @@ def main():
                      "note": "algorithmic contraction work (6D+4Dv FLOP per causal pair) over the "
                              "kernel's mean launch time; the kernel is bound by CUDA-core issue, "
                              "not by the tensor pipe"},
-        "roofline_forward": {"bound": "hbm", "kernels": "pack_symbols+hard_match+gather_output",
+        "roofline_forward": {"bound": "hbm",
+                             "kernels": ("stream_append+stream_match+stream_finish" if kind == "stream"
+                                         else "pack_symbols+hard_match+gather_output"),
                              "achieved": fwd_gbs, "peak": hbm_peak, "unit": "GB/s",
                              "frac": (fwd_gbs / hbm_peak) if fwd_gbs else None},
         "kernel_ms_per_step": {n: ms / args.steps for n, (ms, _) in sorted(kernels.items())},
     }
     if not args.no_cpu_baseline:
-        value, sec, cores, desc = cpu_reference_run(cfg, 1, 0)
+        base_kind = "port"
+        if kind == "stream":
+            value, sec, cores, desc, base_kind = cpu_stream_run(cfg, 1, 1)
+        else:
+            value, sec, cores, desc = cpu_reference_run(cfg, 1, 0)
         result["cpu_baseline"] = {"value": value, "unit": "M token-heads/s", "cores": cores,
-                                  "kind": "port", "sample": desc, "seconds": sec}
+                                  "kind": base_kind, "sample": desc, "seconds": sec}
     print(json.dumps(result))
     if dist is not None:
         dist.destroy_process_group()
