@@ -792,24 +792,24 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_kernel(VjpArgs a) {
 // ------------------------------------------------- sweep 2 on the tensor core
 // Same schedule as vjp_sweep2_kernel, but the three block contractions
 //     dKz[j] += sum_i C(i,j) qz[i]      dVz[j+1] += sum_i (p d)(i,j) gO(i)      dQz[i] += sum_j C(i,j) kz[j]
-// run as tcgen05.mma with fp32 accumulators in tensor memory.  The adjoint phase writes C
-// and p*d as bf16 (high, low) pairs -- 16 mantissa bits, the +-1 operands are exact -- into
-// un-skewed [row][window column] tiles made of 8x16-byte core matrices.  The same tile is
-// read MN-major (M = 128 window columns, K = the 16 block rows) for the column sums and
-// K-major (M = rows, K = window columns) for the row sums; the row-sum MMA uses M = 128 with
-// only the first 16 accumulator rows meaningful (the other rows read whatever follows the
-// tile in shared memory and are never looked at).  The 271-column window is covered by the
-// chunks [0,128), [128,256) and [144,272); only columns >= 256 of the last chunk are used.
+// run as tcgen05.mma with fp32 accumulators in tensor memory.  The adjoint phase writes C as
+// three bf16 terms (24 mantissa bits) and p*d as two (the +-1 operands are exact) into one
+// un-skewed [row][window column] operand area made of 8x16-byte core matrices.  The same bytes
+// are read MN-major (M = 128 window columns, K = the 16 block rows) for the column sums and
+// K-major (M = rows, K = window columns) for the row sums.  The 271-column window is covered by
+// the chunks [0,128), [128,256) and [144,272); only columns >= 256 of the last chunk are used.
 namespace tcl {
-// Core matrices are ordered [column group][row group]: the two row groups of a column group
-// sit 144 bytes apart (128-byte core + 16 bytes of skew against bank conflicts) and column
-// groups 288 bytes apart.  Keeping the row groups close matters for the row-sum MMA, which
-// runs with M = 128 although only 16 rows exist: its 14 surplus row groups then alias the
-// bytes of the following column groups (finite garbage in accumulator rows nobody reads)
-// instead of reaching far beyond the tile.
+// Core matrices are ordered [column group][term][row group]: each of the 34 column groups holds
+// ten 8-row core matrices -- C high, C low, C third term, p*d high, p*d low, two row groups each
+// -- 144 bytes apart (128-byte core + 16 bytes of skew against bank conflicts).  Read K-major
+// with M = 64, the first six of them are the 48 rows (hi; lo; third term) of ONE row-sum
+// operand: a single MMA per k-step multiplies all three terms of C by kz, the three 16-row
+// slices of the accumulator are added on read-back.  (Rows 48-63 alias the p*d cores: finite
+// values in accumulator rows nobody reads.)
 constexpr int kRowGroupBytes = 144;
-constexpr int kColGroupBytes = (kVjpRows / 8) * kRowGroupBytes;
-constexpr int kTileBytes = (kWinCols / 8) * kColGroupBytes;
+constexpr int kTermBytes = (kVjpRows / 8) * kRowGroupBytes;          // one term of one column group
+constexpr int kColGroupBytes = 5 * kTermBytes;
+constexpr int kOperandBytes = (kWinCols / 8) * kColGroupBytes;       // all five terms
 __host__ __device__ constexpr int chunk_start(int ch) { return ch == 0 ? 0 : ch == 1 ? 128 : kWinCols - 128; }
 static_assert(kVjpRows == 16, "one MMA k-step spans exactly the 16 rows of a block");
 __device__ __forceinline__ int tile_off(int r, int c) {
@@ -861,12 +861,14 @@ struct TcSmem {
   static constexpr int kKzSlotBytes = NK * 32;                  // [NK][16] bf16
   static constexpr int kQzBytes = NK * kVjpRows * 2;
   static constexpr int kGBytes = NV * kVjpRows * 2;
-  static constexpr int oQz = 5 * tcl::kTileBytes;               // two buffers
+  static constexpr int oQz = tcl::kOperandBytes;                // two buffers
   static constexpr int oGhi = oQz + 2 * kQzBytes;               // two buffers
   static constexpr int oGlo = oGhi + 2 * kGBytes;               // two buffers
   static constexpr int oKz = oGlo + 2 * kGBytes;
   static constexpr int oBar = oKz + kKzSlots * kKzSlotBytes;
-  static constexpr int kBytes = oBar + 16;
+  static constexpr int oDq = oBar + 16;                         // row-sum terms of two warps
+  static constexpr int kDqFloats = 2 * kVjpRows * 16;
+  static constexpr int kBytes = oDq + kDqFloats * 4;
 };
 
 // Software pipeline per CTA: the MMAs of block b run on the tensor core while the CUDA
@@ -879,13 +881,12 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   using L = TcSmem<NK, NV>;
   extern __shared__ float4 smem_raw[];
   unsigned char* sbase = reinterpret_cast<unsigned char*>(smem_raw);
-  // the three C tiles come first: the row-sum MMA over-reads each of them by 14 row groups
-  // (2 KB), which lands in the tile that follows
   unsigned char* tChi = sbase;                         // C = hi + lo + lo2 (24 mantissa bits)
-  unsigned char* tClo = tChi + tcl::kTileBytes;
-  unsigned char* tCl2 = tClo + tcl::kTileBytes;        // third term of C, row sums only
-  unsigned char* tPhi = tCl2 + tcl::kTileBytes;
-  unsigned char* tPlo = tPhi + tcl::kTileBytes;
+  unsigned char* tClo = tChi + tcl::kTermBytes;
+  unsigned char* tCl2 = tClo + tcl::kTermBytes;        // third term of C, row sums only
+  unsigned char* tPhi = tCl2 + tcl::kTermBytes;        // p*d = hi + lo
+  unsigned char* tPlo = tPhi + tcl::kTermBytes;
+  float* s_dq = reinterpret_cast<float*>(sbase + L::oDq);
   unsigned char* bKz = sbase + L::oKz;
   uint64_t* mbar = reinterpret_cast<uint64_t*>(sbase + L::oBar);
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(mbar + 1);
@@ -912,12 +913,12 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   float* ring = ring_slots ? a.ring + it.item_linear * (int64_t)ring_slots * kVjpBand + tid
                            : nullptr;
   // row-sum k-loop: split over NQ issuing threads, one accumulator each (summed on read-back)
-  constexpr int NQ = NK == 16 ? 4 : 2;
+  constexpr int NQ = 2;
   constexpr uint32_t kTmemCols = ((3 + NQ) * NK + 3 * NV) <= 128 ? 128 : 256;
   constexpr uint32_t kColK = 0, kColV = 3 * NK, kColQ = 3 * NK + 3 * NV;
 
   // ---- one-time set-up
-  for (int e = tid; e < 5 * tcl::kTileBytes / 16; e += kVjpBand)
+  for (int e = tid; e < tcl::kOperandBytes / 16; e += kVjpBand)
     reinterpret_cast<uint4*>(tChi)[e] = make_uint4(0, 0, 0, 0);
   if (tid <= D) {
     const float gate = expf(neg_md * (float)tid);
@@ -987,23 +988,39 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
         }
       }
     }
-    if ((mask & 1) && warp == 4) {
+    if ((mask & 1) && warp >= 4 && warp < 7) {
+      // accumulator rows 0-15 / 16-31 / 32-47 (the three terms of C) sit in lanes 0-15 of the
+      // lane quarters 0 / 1 / 2: warps 4, 5, 6 read one each, warp 4 adds them up
+      const int term = warp - 4;
+      const uint32_t term_base = (uint32_t)(32 * term) << 16;
       for (int n0 = 0; n0 < NK; n0 += 16) {
         float v[16];
-        tc::tmem_ld16(tmem + kColQ + n0, v);   // accumulator rows 0..31 = block rows
+        tc::tmem_ld16(tmem + term_base + kColQ + n0, v);
 #pragma unroll
         for (int part = 1; part < NQ; ++part) {
           float v2[16];
-          tc::tmem_ld16(tmem + kColQ + part * NK + n0, v2);
+          tc::tmem_ld16(tmem + term_base + kColQ + part * NK + n0, v2);
 #pragma unroll
           for (int d = 0; d < 16; ++d) v[d] += v2[d];
         }
-        if (lane < b.nrows) {
+        if (term > 0 && lane < kVjpRows) {
+          float4* dst4 = reinterpret_cast<float4*>(s_dq + ((term - 1) * kVjpRows + lane) * 16);
+#pragma unroll
+          for (int d4 = 0; d4 < 4; ++d4)
+            dst4[d4] = make_float4(v[4 * d4], v[4 * d4 + 1], v[4 * d4 + 2], v[4 * d4 + 3]);
+        }
+        asm volatile("bar.sync 1, 96;" ::: "memory");
+        if (term == 0 && lane < b.nrows) {
+          const float* lo = s_dq + lane * 16;
+          const float* l2 = s_dq + (kVjpRows + lane) * 16;
           float* dst = a.dq_part + (it.rowslot + b.i0 + lane) * D + n0;
 #pragma unroll
-          for (int d = 0; d < 16; ++d)
-            if (n0 + d < D) dst[d] = (b.w == it.w_begin) ? v[d] : dst[d] + v[d];
+          for (int d = 0; d < 16; ++d) {
+            const float sum = v[d] + lo[d] + l2[d];
+            if (n0 + d < D) dst[d] = (b.w == it.w_begin) ? sum : dst[d] + sum;
+          }
         }
+        if (n0 + 16 < NK) asm volatile("bar.sync 1, 96;" ::: "memory");
       }
     }
     tc::fence_before_thread_sync();
@@ -1322,8 +1339,8 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
       tc::fence_after_thread_sync();
       constexpr uint32_t idK = tc::idesc_bf16_f32(128, NK, true, false);
       constexpr uint32_t idV = tc::idesc_bf16_f32(128, NV, true, false);
-      // the row sums need 16 accumulator rows: M = 64 is the smallest shape and halves the
-      // operand bytes the instruction reads from shared memory (rows 0-15 land in lanes 0-15)
+      // the row sums need 48 accumulator rows (three terms x 16 block rows): M = 64, whose row r
+      // lands in lane 32 * (r / 16) + r % 16
       constexpr uint32_t idQ = tc::idesc_bf16_f32(64, NK, false, false);
       if (warp == 0 && (mask & 2)) {
         const uint64_t dQz = tc::smem_desc(tc::smem_addr(bQz), NK / 8 * 128, 128);
@@ -1352,10 +1369,9 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
         }
       }
       if (warp >= 4 - NQ && (mask & 1)) {
-        // K-major view (row sums): K direction = column groups, M direction = row groups
-        const uint64_t kChi = tc::smem_desc(tc::smem_addr(tChi), tcl::kColGroupBytes, tcl::kRowGroupBytes);
-        const uint64_t kClo = tc::smem_desc(tc::smem_addr(tClo), tcl::kColGroupBytes, tcl::kRowGroupBytes);
-        const uint64_t kCl2 = tc::smem_desc(tc::smem_addr(tCl2), tcl::kColGroupBytes, tcl::kRowGroupBytes);
+        // K-major view (row sums): K direction = column groups, M direction = the six row
+        // groups hi0 hi1 lo0 lo1 l20 l21 of a column group (M = 64: two more alias p*d)
+        const uint64_t kC = tc::smem_desc(tc::smem_addr(tChi), tcl::kColGroupBytes, tcl::kRowGroupBytes);
         const uint64_t dKz0 = tc::smem_desc(tc::smem_addr(bKz), NK / 8 * 128, 128);
         constexpr int kSteps = kWinCols / 16;
         const int part = warp - (4 - NQ);                       // this issuer's slice of the k-loop
@@ -1367,9 +1383,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
         for (int ks = ks0; ks < ks1; ++ks) {
           const uint64_t dKz = dKz0 + (uint64_t)((sl * L::kKzSlotBytes) >> 4);
           const uint64_t shift = (uint64_t)((ks * 2 * tcl::kColGroupBytes) >> 4);
-          tc::mma_bf16(acc, kChi + shift, dKz, idQ, ks > ks0);
-          tc::mma_bf16(acc, kClo + shift, dKz, idQ, true);
-          tc::mma_bf16(acc, kCl2 + shift, dKz, idQ, true);
+          tc::mma_bf16(acc, kC + shift, dKz, idQ, ks > ks0);
           sl = sl + 1 == L::kKzSlots ? 0 : sl + 1;
         }
       }
