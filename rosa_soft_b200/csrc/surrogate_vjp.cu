@@ -227,19 +227,33 @@ __device__ __forceinline__ void fill_block_windows(const SweepSmem& sm, const It
   }
 }
 
-// Branch-free forward step of one diagonal: gate, window product, evidence.
-// Inactive cells (before the diagonal starts) leave S and hs at zero.
+// Largest mismatch-count sum whose window product exp(-m * hs / D) is not flushed to zero
+// (the kernels are compiled with flush-to-zero: exp(x) == 0 for x <= -88).
+__device__ __forceinline__ int window_sum_cutoff(float neg_md) {
+  if (!(neg_md < 0.0f)) return 1000000000;
+  const float lim = -88.0f / neg_md;
+  return lim < 1.0e9f ? (int)lim : 1000000000;
+}
+
+// Forward step of one diagonal: gate, window product, evidence.  Inactive cells (before the
+// diagonal starts) leave S and hs at zero.  With kSkipDeadWindow the exponential of the window
+// product is skipped when no lane of the warp has a sum small enough to survive flush-to-zero
+// (all lanes of the warp must then call together); that pays where the special-function unit
+// is loaded (sweep 2) and costs where integer issue binds (sweep 1).
+template <bool kSkipDeadWindow>
 __device__ __forceinline__ float forward_cell(float& S, int& hs, bool act, int qi, int kj,
                                               int qold, int kold, int j, const float* glut,
-                                              bool windowed, int W, float neg_md) {
+                                              bool windowed, int W, float neg_md, int hs_cut) {
   const int ham = __popc(qi ^ kj);
   const float x = glut[ham];
   float P = 0.0f;
   if (windowed) {
     hs += act ? ham : 0;
     hs -= (j > W) ? __popc(qold ^ kold) : 0;
-    const float pw = __expf(neg_md * (float)hs);
-    P = (j >= W) ? pw : 0.0f;
+    if (!kSkipDeadWindow || __any_sync(0xffffffffu, j >= W && hs <= hs_cut)) {
+      const float pw = __expf(neg_md * (float)hs);
+      P = (j >= W) ? pw : 0.0f;
+    }
   }
   const float Sn = x * (1.0f + S) - P;
   S = act ? Sn : 0.0f;
@@ -305,6 +319,7 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
   const int W = a.W;
   const float scale = a.scale, inv_keep = a.inv_keep;
   const float neg_md = -a.mismatch_scale / (float)a.D;
+  const int hs_cut = window_sum_cutoff(neg_md);
   constexpr bool windowed = kWindowed;
   constexpr bool use_dropout = kDropout;
   const DropoutKey dkey = make_dropout_key((uint32_t)it.h + a.head_offset,
@@ -316,8 +331,8 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
   // one cell of the forward sweep: returns (e, e * d * u) and, with dropout, the keep flag
   auto cell = [&](bool act, int r, int c, int j, int i, uint32_t qword, float& S, int& hs,
                   float& e, float& edu, bool& keep) {
-    forward_cell(S, hs, act, sm.s_q[r], sm.s_k[c], sm.s_qold[r], sm.s_kold[c], j, sm.glut,
-                 windowed, W, neg_md);
+    forward_cell<false>(S, hs, act, sm.s_q[r], sm.s_k[c], sm.s_qold[r], sm.s_kold[c], j, sm.glut,
+                        windowed, W, neg_md, hs_cut);
     // the log i term cancels in the softmax, so the fixed reference drops it too
     const float logit = (sqrtf(1.0f + S) - 1.0f) * logit_mul - ref_top;
     const float ex = __expf(logit);
@@ -421,8 +436,8 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
         for (int r = 0; r < nrows; ++r) {
           const bool act = r >= r_first;
           const int c = cbase + r, j = jbase + r, i = i0 + r;
-          forward_cell(S, hs, act, sm.s_q[r], sm.s_k[c], sm.s_qold[r], sm.s_kold[c], j, sm.glut,
-                       windowed, W, neg_md);
+          forward_cell<false>(S, hs, act, sm.s_q[r], sm.s_k[c], sm.s_qold[r], sm.s_kold[c], j,
+                              sm.glut, windowed, W, neg_md, hs_cut);
           const float logit = act ? kSqrtScale * (sqrtf(1.0f + S) - 1.0f) * scale - sm.rstat[r].w
                                   : -CUDART_INF_F;
           float du = cell_utility<kSmallDv>(a, it, sm, vb, act, i, j, r, c, ngroups);
@@ -542,6 +557,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_kernel(VjpArgs a) {
   const int W = a.W, D = a.D, mask = a.mask, ring_slots = a.ring_slots;
   const float scale = a.scale, inv_keep = a.inv_keep;
   const float neg_md = -a.mismatch_scale / (float)a.D;
+  const int hs_cut = window_sum_cutoff(neg_md);
   const bool windowed = W <= it.len - 2;
   const bool use_dropout = a.dropout_p > 0.0f;
   const float4* __restrict__ rowstat = a.rowstat + (int64_t)it.h * a.N + it.start;
@@ -598,8 +614,9 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_kernel(VjpArgs a) {
 #pragma unroll 4
       for (int r = 0; r < nrows; ++r) {
         const int c = cbase + r;
-        const float P = forward_cell(S, hs, r >= r_first, sm.s_q[r], sm.s_k[c], sm.s_qold[r],
-                                     sm.s_kold[c], jbase + r, sm.glut, windowed, W, neg_md);
+        const float P = forward_cell<true>(S, hs, r >= r_first, sm.s_q[r], sm.s_k[c], sm.s_qold[r],
+                                           sm.s_kold[c], jbase + r, sm.glut, windowed, W, neg_md,
+                                           hs_cut);
         has_p |= P != 0.0f;
         Cbuf[r * kVjpBand + tid] = S;
         Pbuf[r * kVjpBand + tid] = P;
@@ -848,6 +865,8 @@ __host__ __device__ constexpr int tc_table_floats(int ngroups, int NV) {
          4 * kWinCols + kVjpRows * NV + 2 * kVjpBand;
 }
 
+constexpr bool kSkipTc = true;   // forward phase of the tensor-core kernel skips dead windows
+
 // geometry of one row block, kept in registers for the deferred epilogue
 struct TcBlock {
   int w, rb, i0, nrows, jwin, dmin, dmax;
@@ -908,6 +927,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   const int W = a.W, D = a.D, Dv = a.Dv, mask = a.mask, ring_slots = a.ring_slots;
   const float scale = a.scale, inv_keep = a.inv_keep;
   const float neg_md = -a.mismatch_scale / (float)a.D;
+  const int hs_cut = window_sum_cutoff(neg_md);
   const bool has_glo = a.dtype != ROSA_B200_BF16;   // bf16 grad_output is exact in one term
   const float4* __restrict__ rowstat = a.rowstat + (int64_t)it.h * a.N + it.start;
   float* ring = ring_slots ? a.ring + it.item_linear * (int64_t)ring_slots * kVjpBand + tid
@@ -1045,6 +1065,15 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     return g;
   };
   const int rb_top = (it.len - 1) / kVjpRows;    // bottom row block of every band
+  // The route probability of a cell is exp(logit - log i - max) / Z with
+  // logit = c * scale * (sqrt(1 + S) - 1); the tables keep it ready for one fused
+  // multiply-add and a base-2 exponential: p = exp2(sqrt(1 + S) * mul2 + bias) / Z,
+  // bias = -(log i + max) * log2(e) - mul2 stored in place of the row maximum.
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float mul2 = kSqrtScale * scale * kLog2e;
+  auto exponent_bias = [&](float row_max, float log_i) {
+    return -(log_i + row_max) * kLog2e - mul2;
+  };
   auto go_value = [&](const Geom& g, int e) {
     const int r = e / NV, d = e - r * NV;
     return (d < Dv && r < g.nrows)
@@ -1054,7 +1083,11 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   // straight global -> shared fill of one table set (first block of a band)
   auto fill_direct = [&](const Geom& g, const SweepSmem& t) {
     fill_block_windows<true>(t, it, q, k, vb, g.i0, g.nrows, g.jwin, kWinCols, kWindowed, W, false);
-    if (tid < g.nrows) t.rstat[tid] = rowstat[g.i0 + tid];
+    if (tid < g.nrows) {
+      float4 st = rowstat[g.i0 + tid];
+      st.x = exponent_bias(st.x, st.w);
+      t.rstat[tid] = st;
+    }
     if (kDropout && tid < g.nrows * kVjpWarps)
       t.s_keep[tid] = a.keepbits[(g.ck_idx * kVjpRows) * kVjpWarps + tid];
     for (int e = tid; e < kVjpRows * NV; e += kVjpBand) t.rest[e] = go_value(g, e);
@@ -1132,9 +1165,14 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
         const int r = tid - 48;
         pf0 = r < gn.nrows ? (uint32_t)__ldg(q + gn.i0 + r) : 0u;
       } else if (tid < 128) {
+        // component e & 3 of row e >> 2; the maximum (component 0) becomes the exponent bias,
+        // which needs log i (component 3) from three lanes up
         const int e = tid - 64;
-        if ((e >> 2) < gn.nrows)
-          pf0 = __float_as_uint(reinterpret_cast<const float*>(rowstat + gn.i0)[e]);
+        float comp = 0.0f;
+        if ((e >> 2) < gn.nrows) comp = reinterpret_cast<const float*>(rowstat + gn.i0)[e];
+        const float log_i = __shfl_down_sync(0xffffffffu, comp, 3);
+        if ((e & 3) == 0) comp = exponent_bias(comp, log_i);
+        pf0 = __float_as_uint(comp);
       } else if (kDropout) {
         const int e = tid - 128;
         if (e < gn.nrows * kVjpWarps) pf0 = a.keepbits[(gn.ck_idx * kVjpRows) * kVjpWarps + e];
@@ -1198,8 +1236,9 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
 #pragma unroll 4
     for (int r = 0; r < nrows; ++r) {
       const int c = cbase + r;
-      const float P = forward_cell(S, hs, r >= r_first, sm.s_q[r], sm.s_k[c], sm.s_qold[r],
-                                   sm.s_kold[c], jbase + r, sm.glut, kWindowed, W, neg_md);
+      const float P = forward_cell<kSkipTc>(S, hs, r >= r_first, sm.s_q[r], sm.s_k[c], sm.s_qold[r],
+                                            sm.s_kold[c], jbase + r, sm.glut, kWindowed, W, neg_md,
+                                            hs_cut);
       has_p |= P != 0.0f;
       Sbuf[r * kVjpBand + tid] = S;
     }
@@ -1246,11 +1285,12 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
 
     // ---- phase B: adjoint recurrence, rows descending; C and p*d go to the operand tiles
     const bool warp_p = kWindowed && ring != nullptr && __any_sync(0xffffffffu, has_p);
+    const float ds_mul = scale * (0.5f * kSqrtScale);
     auto seed = [&](bool act, int r, int c, float Sv, float* pd) {
-      const float4 st = sm.rstat[r];
-      const float sq = sqrtf(1.0f + Sv);
-      const float logit = kSqrtScale * (sq - 1.0f) * scale - st.w;
-      const float pr = act ? __expf(logit - st.x) * st.y : 0.0f;
+      const float4 st = sm.rstat[r];                  // (exponent bias, 1/Z, E, log i)
+      const float t = 1.0f + Sv;
+      const float rs = rsqrtf(t);                     // R'(S) = c / (2 sqrt(1 + S))
+      const float pr = act ? exp2f(fmaf(t * rs, mul2, st.x)) * st.y : 0.0f;
       float dmul = 1.0f;
       if (kDropout) dmul = (sm.s_keep[r * kVjpWarps + warp] >> lane & 1u) ? inv_keep : 0.0f;
       const uint32_t bits = sm.s_vb[c];
@@ -1260,25 +1300,33 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
       for (int gq = 0; gq < NG; ++gq) u += lut[gq * 16 + ((bits >> (4 * gq)) & 15u)];
       *pd = pr * dmul;
       const float dlogit = *pd * u - pr * st.z;
-      return scale * dlogit * (0.5f * kSqrtScale) * __frcp_rn(sq);
+      return ds_mul * dlogit * rs;
     };
     if (!warp_p && live == 0) {
-      // no window product is alive in this warp: P = 0, T = 0, Y = 0, C = S * Sbar
+      // No window product is alive in this warp: P = 0, T = 0, Y = 0, C = S * Sbar.  The adjoint
+      // recurrence Sbar <- dS + x * Sbar is a contraction here and runs in float32 inside the
+      // block; the tile offset walks down the diagonal incrementally.
+      float sb = (float)Sbar;
+      int c = cbase + nrows - 1;
+      int off = tcl::tile_off(nrows - 1, c);
 #pragma unroll 4
       for (int r = nrows - 1; r >= 0; --r) {
         const bool act = r >= r_first;
-        const int c = cbase + r;
         const float Sv = Sbuf[r * kVjpBand + tid];
         const float x = sm.glut[__popc(sm.s_q[r] ^ sm.s_k[c])];
         float pd;
         const float dS = seed(act, r, c, Sv, &pd);
-        Sbar = (double)dS + (double)xnext * Sbar;
-        const float Cv = act ? Sv * (float)Sbar : 0.0f;
-        const int off = tcl::tile_off(r, c);
+        sb = fmaf(xnext, sb, dS);
+        const float Cv = act ? Sv * sb : 0.0f;
         tcl::store_split3(tChi, tClo, tCl2, off, Cv);
         tcl::store_split(tPhi, tPlo, off, pd);
         xnext = x;
+        // one row up, one column left: -16 - 2 inside a core matrix, else hop to the previous
+        // row group (-144 + 7 * 16) / column group (-kColGroupBytes + 7 * 2)
+        off -= ((r & 7) ? 16 : tcl::kRowGroupBytes - 112) + ((c & 7) ? 2 : tcl::kColGroupBytes - 14);
+        --c;
       }
+      Sbar = (double)sb;
       if (valid && ring_slots) {
         slot -= (nrows - r_first) % ring_slots;
         if (slot < 0) slot += ring_slots;
