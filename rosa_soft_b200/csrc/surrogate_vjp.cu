@@ -825,7 +825,10 @@ namespace tcl {
 // values in accumulator rows nobody reads.)
 constexpr int kRowGroupBytes = 144;
 constexpr int kTermBytes = (kVjpRows / 8) * kRowGroupBytes;          // one term of one column group
-constexpr int kColGroupBytes = 5 * kTermBytes;
+// 16 bytes of padding make the column-group stride 364 words = 12 (mod 32): a warp's row of 32
+// consecutive columns touches up to five column groups, whose 16-byte rows then fall into
+// five disjoint sets of four banks
+constexpr int kColGroupBytes = 5 * kTermBytes + 16;
 constexpr int kOperandBytes = (kWinCols / 8) * kColGroupBytes;       // all five terms
 __host__ __device__ constexpr int chunk_start(int ch) { return ch == 0 ? 0 : ch == 1 ? 128 : kWinCols - 128; }
 static_assert(kVjpRows == 16, "one MMA k-step spans exactly the 16 rows of a block");
