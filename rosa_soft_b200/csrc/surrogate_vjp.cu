@@ -870,12 +870,6 @@ __host__ __device__ constexpr int tc_table_floats(int ngroups, int NV) {
 
 constexpr bool kSkipTc = true;   // forward phase of the tensor-core kernel skips dead windows
 
-// geometry of one row block, kept in registers for the deferred epilogue
-struct TcBlock {
-  int w, rb, i0, nrows, jwin, dmin, dmax;
-  bool pending;
-};
-
 // Shared-memory plan of the tensor-core kernel (bytes from the start of dynamic smem).
 template <int NK, int NV>
 struct TcSmem {
@@ -957,11 +951,31 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   uint32_t mma_phase = 0;
   bool mma_timed_out = false;
   int buf = 0;                       // B-operand buffer of the block being built
-  TcBlock prev;
-  prev.pending = false;
+  // ---- the blocks of this CTA as one flat sequence: bands ascending, row blocks descending
+  struct Geom {
+    int w, rb, rb_lo, i0, nrows, jwin, dmin, dmax;
+    int64_t ck_idx;
+  };
+  auto geom_of = [&](int w, int rb) {
+    Geom g;
+    g.w = w;
+    g.rb = rb;
+    g.dmin = 1 + w * kVjpBand;
+    g.dmax = g.dmin + kVjpBand - 1;
+    g.rb_lo = g.dmin / kVjpRows;
+    g.i0 = max(rb * kVjpRows, g.dmin);
+    g.nrows = min(rb * kVjpRows + kVjpRows - 1, it.len - 1) - g.i0 + 1;
+    g.jwin = rb * kVjpRows - g.dmax;             // window start, a multiple of 16
+    g.ck_idx = it.ck_base + vjp_ck_before(it.len, w) + (rb - g.rb_lo);
+    return g;
+  };
+  // the block whose MMAs are in flight; its geometry is recomputed when they are collected
+  int prev_w = 0, prev_rb = 0;
+  bool prev_pending = false;
 
   // Reads the accumulators of a finished block and adds them to the per-item partials.
-  auto epilogue = [&](const TcBlock& b) {
+  auto epilogue = [&](int block_w, int block_rb) {
+    const Geom b = geom_of(block_w, block_rb);
     if (!tc::mbar_wait(mbar, mma_phase, 1u << 24)) mma_timed_out = true;
     mma_phase ^= 1u;
     tc::fence_after_thread_sync();
@@ -1049,24 +1063,6 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     tc::fence_before_thread_sync();
   };
 
-  // ---- the blocks of this CTA as one flat sequence: bands ascending, row blocks descending
-  struct Geom {
-    int w, rb, rb_lo, i0, nrows, jwin, dmin, dmax;
-    int64_t ck_idx;
-  };
-  auto geom_of = [&](int w, int rb) {
-    Geom g;
-    g.w = w;
-    g.rb = rb;
-    g.dmin = 1 + w * kVjpBand;
-    g.dmax = g.dmin + kVjpBand - 1;
-    g.rb_lo = g.dmin / kVjpRows;
-    g.i0 = max(rb * kVjpRows, g.dmin);
-    g.nrows = min(rb * kVjpRows + kVjpRows - 1, it.len - 1) - g.i0 + 1;
-    g.jwin = rb * kVjpRows - g.dmax;             // window start, a multiple of 16
-    g.ck_idx = it.ck_base + vjp_ck_before(it.len, w) + (rb - g.rb_lo);
-    return g;
-  };
   const int rb_top = (it.len - 1) / kVjpRows;    // bottom row block of every band
   // The route probability of a cell is exp(logit - log i - max) / Z with
   // logit = c * scale * (sqrt(1 + S) - 1); the tables keep it ready for one fused
@@ -1097,9 +1093,9 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     reinterpret_cast<int2*>(t.rest + kVjpRows * NV)[tid] = a.ckpt[g.ck_idx * kVjpBand + tid];
   };
 
-  Geom g = geom_of(it.w_begin, rb_top);
-  int tb = 0;                                    // table set of the block being computed
-  fill_direct(g, carve_common(tab_base, NG));
+  int w = it.w_begin, rb = rb_top;               // the block being computed
+  int tb = 0;                                    // its table set
+  fill_direct(geom_of(w, rb), carve_common(tab_base, NG));
   __syncthreads();
 
   // per-band state of this thread's diagonal
@@ -1113,7 +1109,8 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     const SweepSmem nx = carve_common(tab_base + (tb ^ 1) * kTabFloats, NG);
     const float* s_go = sm.rest;                                     // [kVjpRows][NV]
     const int2* s_ck = reinterpret_cast<const int2*>(sm.rest + kVjpRows * NV);
-    const int w = g.w, rb = g.rb, i0 = g.i0, nrows = g.nrows, jwin = g.jwin;
+    const Geom g = geom_of(w, rb);
+    const int i0 = g.i0, nrows = g.nrows, jwin = g.jwin;
     const int dmin = g.dmin, dmax = g.dmax;
     const int skew = i0 - rb * kVjpRows;         // 1 on the top block of a band, else 0
     if (band_start) {
@@ -1127,16 +1124,14 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
       slot = (valid && ring_slots) ? (it.len - 1 - delta) % ring_slots : 0;
       // the bottom block of a band refills the whole kz^T ring: the last block of the
       // previous band must have released it
-      if (prev.pending) {
-        epilogue(prev);
-        prev.pending = false;
+      if (prev_pending) {
+        epilogue(prev_w, prev_rb);
+        prev_pending = false;
       }
     }
     // the block after this one
     const bool next_same = rb > g.rb_lo;
     const bool has_next = next_same || w + 1 < it.w_end;
-    Geom gn = g;
-    if (has_next) gn = next_same ? geom_of(w, rb - 1) : geom_of(w + 1, rb_top);
 
     unsigned char* bQz = sbase + L::oQz + buf * L::kQzBytes;
     unsigned char* bGhi = sbase + L::oGhi + buf * L::kGBytes;
@@ -1153,6 +1148,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     float pgo[kGoRegs];
     int2 pck = make_int2(0, 0);
     if (next_same) {
+      const Geom gn = geom_of(w, rb - 1);
       if (tid < 16) {
         const int j = gn.jwin + tid;
         pf0 = (j >= 0 && j < it.len - 1) ? (uint32_t)__ldg(k + j) : 0u;
@@ -1273,11 +1269,11 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
       }
       reinterpret_cast<int2*>(nx.rest + kVjpRows * NV)[tid] = pck;
     } else if (has_next) {
-      fill_direct(gn, nx);
+      fill_direct(geom_of(w + 1, rb_top), nx);
     }
 
     // ---- the previous block's MMAs have had the whole table/forward phase to finish
-    if (prev.pending) epilogue(prev);
+    if (prev_pending) epilogue(prev_w, prev_rb);
     // rows of a partial block that do not exist contribute nothing
     for (int r = nrows; r < kVjpRows; ++r) {
       const int off = tcl::tile_off(r, cbase + r);
@@ -1440,8 +1436,9 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
       }
       tc::mma_commit(mbar);
     }
-    prev.w = w; prev.rb = rb; prev.i0 = i0; prev.nrows = nrows; prev.jwin = jwin;
-    prev.dmin = dmin; prev.dmax = dmax; prev.pending = true;
+    prev_w = w;
+    prev_rb = rb;
+    prev_pending = true;
     buf ^= 1;
     // leave the ring zeroed for the next band of this item
     if (!next_same && ring != nullptr && ring_dirty && has_next) {
@@ -1449,10 +1446,15 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     }
     if (!has_next) break;
     band_start = !next_same;
-    g = gn;
+    if (next_same) {
+      --rb;
+    } else {
+      ++w;
+      rb = rb_top;
+    }
     tb ^= 1;
   }
-  if (prev.pending) epilogue(prev);
+  if (prev_pending) epilogue(prev_w, prev_rb);
   __syncthreads();
   if (mma_timed_out && tid == 0) atomicExch(a.plan.status + 1, 1);
   if (warp == 0) tc::tmem_dealloc(tmem, kTmemCols);
