@@ -1,7 +1,7 @@
 """Compile the reference's own RosaRuntime (CPU suffix automaton) into oracle/_ref/.
 
 The single source file is compiled where it lies in the mounted reference tree
-(``$ROSA_REFERENCE_ROOT``, default ``/root/reference``); nothing is copied into
+(``$ROSA_REFERENCE_ROOT``, or the default mount point below); nothing is copied into
 this repository and the output directory is git-ignored.  The shared object is
 used by the tests to validate the oracle's restatement of the match semantics
 and by the benchmark as the reference CPU baseline of the hard-inference path.

@@ -1,7 +1,7 @@
 """Generate golden input/output vectors by running the UNMODIFIED reference.
 
-Run in a container where the reference tree is mounted (default
-``/root/reference``):  ``python tests/golden/make_golden.py``.
+Run in a container where the reference tree is mounted (``$ROSA_REFERENCE_ROOT``, or the
+default mount point below):  ``python tests/golden/make_golden.py``.
 It imports ``rosa_soft`` from that tree (pure-PyTorch ``reference`` variant, CPU)
 and, when ``oracle/_ref/librosa_runtime_ref.so`` has been built by
 ``oracle/build_ref.py``, the reference's own RosaRuntime.  The ``.npz`` files it
