@@ -326,6 +326,9 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
                                            (uint32_t)it.seq + a.batch_offset, a.seed, a.dropout_p);
   const float ref_top = scale * kSqrtScale * (sqrtf(1.0f + (float)W) - 1.0f);
   const float logit_mul = kSqrtScale * scale;
+  // exp(logit - ref_top) as one fused multiply-add and a base-2 exponential of sqrt(1 + S)
+  const float mul2 = logit_mul * 1.4426950408889634f;
+  const float bias2 = -(logit_mul + ref_top) * 1.4426950408889634f;
   if (tid <= a.D) sm.glut[tid] = expf(neg_md * (float)tid);
 
   // one cell of the forward sweep: returns (e, e * d * u) and, with dropout, the keep flag
@@ -334,8 +337,7 @@ __global__ void __launch_bounds__(kVjpBand) vjp_sweep1_kernel(VjpArgs a) {
     forward_cell<false>(S, hs, act, sm.s_q[r], sm.s_k[c], sm.s_qold[r], sm.s_kold[c], j, sm.glut,
                         windowed, W, neg_md, hs_cut);
     // the log i term cancels in the softmax, so the fixed reference drops it too
-    const float logit = (sqrtf(1.0f + S) - 1.0f) * logit_mul - ref_top;
-    const float ex = __expf(logit);
+    const float ex = exp2f(fmaf(sqrtf(1.0f + S), mul2, bias2));
     e = act ? ex : 0.0f;
     float du;
     if (kSmallDv) {
