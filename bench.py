@@ -199,6 +199,13 @@ def make_stream_inputs(cfg, seed, device):
     return to(q), to(k), to(payload)
 
 
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_stream_run(cfg, steps, warmup):
     """The reference's own RosaRuntime (suffix automata on the host cores, compiled from its
     source into oracle/_ref/) fed the same chunks; the oracle's one-shot matcher when that
@@ -212,6 +219,7 @@ def cpu_stream_run(cfg, steps, warmup):
     lib = os.path.join(ROOT, "oracle", "_ref", "librosa_runtime_ref.so")
     times = []
     if os.path.exists(lib):
+        torch.set_num_threads(host_cores())   # torchrun exports OMP_NUM_THREADS=1
         torch.classes.load_library(lib)
         runtime = torch.classes.rosa_soft.RosaRuntime(H, sample["Hv"], sample["D"], sample["Dv"],
                                                       sample["W"])
@@ -229,6 +237,7 @@ def cpu_stream_run(cfg, steps, warmup):
         what = "the reference's RosaRuntime (suffix automata, OpenMP over slot x head)"
     else:
         from oracle import rosa_oracle as orc
+        orc.set_num_threads(host_cores())
         cu = np.arange(B + 1, dtype=np.int64) * T
         flat = lambda x: x.numpy().reshape((B * T,) + tuple(x.shape[2:]))
         for it in range(warmup + steps):
@@ -251,6 +260,7 @@ def cpu_reference_run(cfg, steps, warmup):
 
     from oracle import rosa_oracle as orc
 
+    orc.set_num_threads(host_cores())   # torchrun exports OMP_NUM_THREADS=1
     if cfg.get("kind") == "inference":
         sample = dict(cfg, B=4, T=4096, H=8, Hv=8)
         qs, ks, pay = (t.numpy() for t in make_inference_inputs(sample, 7, "cpu"))
@@ -509,10 +519,10 @@ def main():
         "roofline": {"bound": "tensor", "kernel": "vjp_sweep2", "achieved": achieved,
                      "peak": tensor_peak, "unit": "TFLOP/s",
                      "frac": (achieved / tensor_peak) if achieved else None,
-                     # dram__bytes_read + dram__bytes_write of one launch: 0.977 B per causal pair,
+                     # dram__bytes_read + dram__bytes_write of one launch: 0.979 B per causal pair,
                      # captured with ncu on the `profile` workload (268.4 M pairs) and scaled by
                      # pairs -- checkpoints, keep ballots and partials all grow with the pairs
-                     "traffic": (0.977 * pairs) if flop else None,
+                     "traffic": (0.979 * pairs) if flop else None,
                      "peak_source": peak_note,
                      "note": "algorithmic contraction work (6D+4Dv FLOP per causal pair) over the "
                              "kernel's mean launch time; the kernel is bound by CUDA-core issue, "
@@ -524,7 +534,7 @@ def main():
                              "frac": (fwd_gbs / hbm_peak) if fwd_gbs else None},
         "kernel_ms_per_step": {n: ms / args.steps for n, (ms, _) in sorted(kernels.items())},
     }
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:   # the CPU baseline is reported at N=1 only
         base_kind = "port"
         if kind == "stream":
             value, sec, cores, desc, base_kind = cpu_stream_run(cfg, 1, 1)

@@ -409,6 +409,15 @@ ORACLE_API void oracle_surrogate_vjp(const float* q, const float* k, const float
   free(ks);
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; a timed baseline asks for the cores. */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 ORACLE_API int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -68,6 +68,11 @@ def num_threads() -> int:
     return int(_load().oracle_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """OpenMP threads of the following oracle calls (launchers may have exported OMP_NUM_THREADS=1)."""
+    _load().oracle_set_num_threads(ctypes.c_int(int(n)))
+
+
 def hash_counter(x: int) -> int:
     return int(_load().oracle_hash_counter(ctypes.c_uint32(x & 0xFFFFFFFF)))
 
