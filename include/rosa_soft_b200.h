@@ -119,6 +119,18 @@ ROSA_B200_API int rosa_b200_surrogate_vjp(const void* query, const void* key, co
                             float* grad_query, float* grad_key, float* grad_value, void* workspace,
                             size_t workspace_bytes, void* stream);
 
+/* Inspection of the routing decided by the preceding rosa_b200_hard_forward call on the same
+ * `workspace` (same N, H, num_seq) and stream: per token-head the selected route as a position
+ * local to its sequence (a in [1, i]; 0 = null route) and the exact match length that won
+ * (0 for null).  These are `selected_route_indices` and the winning entry of
+ * `exact_suffix_lengths` of the reference's inspect_rosa_soft (rosa_soft/testing.py:49-117,
+ * rosa_soft/soft_reference.py:295-333) without its [B, H, T, T + 1] tensors: the winners are
+ * already in the workspace, so no matching pass is repeated.  Either output may be NULL. */
+ROSA_B200_API int rosa_b200_hard_forward_routes(const void* workspace, size_t workspace_bytes,
+                                                int64_t N, int H, int64_t num_seq,
+                                                int32_t* selected_route, int32_t* match_length,
+                                                void* stream);
+
 /* --------------------------------------------------------- hard inference batch
  * GPU equivalent of feeding whole streams to RosaRuntime.update_packed
  * (reference rosa_soft/csrc/rosa_runtime.cpp:333-482; match semantics :41-45,

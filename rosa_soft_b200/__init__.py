@@ -69,13 +69,16 @@ BUILD_CAPABILITIES = BuildCapabilities(
 )
 
 from .inference import rosa_hard_inference  # noqa: E402
+from .inspection import HardRouteInspection, inspect_hard_routes  # noqa: E402
 from .runtime import RosaRuntime  # noqa: E402
 from .soft import rosa_soft, rosa_soft_varlen  # noqa: E402
 
 __all__ = [
     "__version__",
     "BUILD_CAPABILITIES",
+    "HardRouteInspection",
     "RosaRuntime",
+    "inspect_hard_routes",
     "rosa_hard_inference",
     "rosa_soft",
     "rosa_soft_varlen",

@@ -20,6 +20,7 @@ EXPORTED_SYMBOLS = (
     "rosa_b200_hard_forward_workspace_bytes",
     "rosa_b200_hard_forward",
     "rosa_b200_hard_forward_static",
+    "rosa_b200_hard_forward_routes",
     "rosa_b200_surrogate_vjp_workspace_bytes",
     "rosa_b200_surrogate_vjp",
     "rosa_b200_hard_inference_workspace_bytes",
@@ -53,6 +54,8 @@ def load() -> ctypes.CDLL:
     lib.rosa_b200_hard_forward_static.restype = i32
     lib.rosa_b200_hard_forward_static.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, i32, vp, i64,
                                                   i64, i64, vp, vp, vp, vp, vp]
+    lib.rosa_b200_hard_forward_routes.restype = i32
+    lib.rosa_b200_hard_forward_routes.argtypes = [vp, sz, i64, i32, i64, vp, vp, vp]
     lib.rosa_b200_surrogate_vjp_workspace_bytes.restype = sz
     lib.rosa_b200_surrogate_vjp_workspace_bytes.argtypes = [i64, i32, i32, i32, i32, i64, i64, i64,
                                                             i32]
@@ -140,6 +143,19 @@ def hard_forward(q, k, v, cu_seqlens, max_suffix_length, want_routes=True, strea
                                      _ptr(pq), _ptr(pk), _ptr(routes), _ptr(ws), nbytes,
                                      ctypes.c_void_p(st)))
     return out, pq, pk, routes, ws
+
+
+def hard_forward_routes(ws, N, H, num_seq, stream=None):
+    """Selected route (local position, 0 = null) and winning match length, int32 [N, H], of the
+    :func:`hard_forward` call that filled the workspace ``ws``."""
+    import torch
+
+    route = torch.empty((N, H), dtype=torch.int32, device=ws.device)
+    length = torch.empty((N, H), dtype=torch.int32, device=ws.device)
+    st = stream if stream is not None else torch.cuda.current_stream(ws.device).cuda_stream
+    check(load().rosa_b200_hard_forward_routes(_ptr(ws), ws.numel(), N, H, num_seq, _ptr(route),
+                                               _ptr(length), ctypes.c_void_p(st)))
+    return route, length
 
 
 def hard_forward_static(q, k, v, cu_seqlens, max_suffix_length, stream=None):

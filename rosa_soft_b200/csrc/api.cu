@@ -187,6 +187,21 @@ ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, con
   return launch_gather_output(a, st);
 }
 
+ROSA_B200_API int rosa_b200_hard_forward_routes(const void* workspace, size_t workspace_bytes,
+                                                int64_t N, int H, int64_t num_seq,
+                                                int32_t* selected_route, int32_t* match_length,
+                                                void* stream) {
+  ROSA_REQUIRE(workspace != nullptr, "null pointer argument");
+  ROSA_REQUIRE(N >= 0 && H >= 1 && num_seq >= 1, "invalid problem size");
+  const FwdLayout l = fwd_layout(N, H, num_seq, false);
+  ROSA_REQUIRE(workspace_bytes >= l.bytes, "workspace too small: need %zu bytes, got %zu", l.bytes,
+               workspace_bytes);
+  if (N == 0 || (selected_route == nullptr && match_length == nullptr)) return 0;
+  const unsigned long long* best = reinterpret_cast<const unsigned long long*>(
+      static_cast<const char*>(workspace) + l.best_off);
+  return launch_route_inspect(best, N * (int64_t)H, selected_route, match_length, as_stream(stream));
+}
+
 ROSA_B200_API size_t rosa_b200_hard_inference_workspace_bytes(int64_t N, int H, int64_t num_seq) {
   return fwd_layout(N, H, num_seq, true).bytes;
 }

@@ -279,6 +279,8 @@ int launch_pack_symbols(const void* q, const void* k, int dtype, int64_t N, int 
                         cudaStream_t stream);
 int launch_hard_match(const FwdArgs& a, int items_upper, cudaStream_t stream);
 int launch_gather_output(const FwdArgs& a, cudaStream_t stream);
+int launch_route_inspect(const unsigned long long* best, int64_t count, int32_t* route,
+                         int32_t* length, cudaStream_t stream);
 int launch_inference_finish(const Plan& plan, const unsigned long long* best, const float* payload,
                             int64_t N, int H, int Hp, int Dp, float* out, int64_t* matched_end,
                             cudaStream_t stream);

@@ -288,7 +288,27 @@ __global__ void inference_finish_kernel(Plan plan, const unsigned long long* __r
   }
 }
 
+// Splits the winners into the selected route (local index a, 0 = null) and its match length.
+__global__ void route_inspect_kernel(const unsigned long long* __restrict__ best, int64_t count,
+                                     int32_t* __restrict__ route, int32_t* __restrict__ length) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= count) return;
+  const unsigned long long key = best[idx];
+  if (route) route[idx] = (int32_t)(key & 0xffffffffull);
+  if (length) length[idx] = (int32_t)(key >> 32);
+}
+
 }  // namespace
+
+int launch_route_inspect(const unsigned long long* best, int64_t count, int32_t* route,
+                         int32_t* length, cudaStream_t stream) {
+  ProfileScope prof("route_inspect", stream);
+  const int threads = 256;
+  route_inspect_kernel<<<(unsigned)((count + threads - 1) / threads), threads, 0, stream>>>(
+      best, count, route, length);
+  ROSA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 int launch_pack_symbols(const void* q, const void* k, int dtype, int64_t N, int H, int D,
                         int dense, int64_t uniform_len, int32_t* pq, int32_t* pk,

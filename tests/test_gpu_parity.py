@@ -430,3 +430,37 @@ def test_operator_error_messages(ops):
         torch.ops.rosa_soft.surrogate_vjp_masked(q, q, v, out, pq, pk, empty, 4, 1.0, 0.5, 3.0, 7)
     with pytest.raises(RuntimeError, match=r"gradient_mask must be an integer bit mask in \[1, 7\]"):
         torch.ops.rosa_soft.surrogate_vjp_masked(q, q, v, out, pq, pk, empty, 4, 1.0, 0.0, 3.0, 0)
+
+
+def test_route_inspection_matches_oracle_dense_and_packed():
+    """Selected routes and winning match lengths come out of the forward's own winners
+    (reference: selected_route_indices / exact_suffix_lengths of rosa_soft/testing.py:49-117)."""
+    import rosa_soft_b200 as rs
+    from oracle import rosa_oracle as orc
+    B, T, H, D, Hv, Dv, W = 2, 333, 4, 2, 2, 8, 24
+    q = nonzero_randn((B, T, H, D), 1, torch.float32)
+    k = torch.where(torch.rand(B, T, H, D, generator=torch.Generator().manual_seed(3)) < 0.8, q, -q)
+    v = nonzero_randn((B, T, Hv, Dv), 2, torch.float32)
+    flat = lambda t: t.reshape(B * T, *t.shape[2:]).numpy()
+    cu = np.arange(B + 1) * T
+    qs, ks = orc.pack_symbols(flat(q)), orc.pack_symbols(flat(k))
+    want_route, want_len = orc.hard_routes(qs, ks, cu, W)
+    want_out, _ = orc.hard_forward(flat(q), flat(k), flat(v), cu, W)
+    out, info = rs.inspect_hard_routes(q.to(DEV), k.to(DEV), v.to(DEV), max_suffix_length=W)
+    assert info.selected_route_indices.shape == (B, H, T) and info.effective_max_suffix_length == W
+    got_route = info.selected_route_indices.permute(0, 2, 1).reshape(B * T, H).cpu().numpy()
+    got_len = info.selected_match_lengths.permute(0, 2, 1).reshape(B * T, H).cpu().numpy()
+    assert np.array_equal(got_route, want_route) and np.array_equal(got_len, want_len)
+    assert np.array_equal(out.reshape(B * T, H, Dv).cpu().numpy(), want_out)
+    assert (got_len[got_route == 0] == 0).all() and got_len.max() <= W
+    assert 0.0 <= info.null_route_fraction < 1.0 and info.mean_match_length >= 1.0
+    # packed: ragged sequences with an empty one
+    lengths = [100, 0, 233, 1, 332]
+    cu_p = np.concatenate([[0], np.cumsum(lengths)])
+    want_route, want_len = orc.hard_routes(qs, ks, cu_p, W)
+    _, info = rs.inspect_hard_routes(q.reshape(B * T, H, D).to(DEV), k.reshape(B * T, H, D).to(DEV),
+                                     v.reshape(B * T, Hv, Dv).to(DEV),
+                                     torch.from_numpy(cu_p.astype(np.int32)).to(DEV),
+                                     max_suffix_length=W)
+    assert np.array_equal(info.selected_route_indices.t().cpu().numpy(), want_route)
+    assert np.array_equal(info.selected_match_lengths.t().cpu().numpy(), want_len)
