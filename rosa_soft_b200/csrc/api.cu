@@ -20,9 +20,12 @@ constexpr size_t kPartialBudgetBytes = (size_t)6 << 30;  // target size of the V
 
 struct FwdLayout {
   PlanLayout plan;
-  size_t best_off, qt_off, kt_off;
+  size_t best_off, qt_off, kt_off, masks_off;
+  int64_t mask_words;
   size_t bytes;
 };
+
+constexpr int kMaskSymbolBits = 8;   // widest symbol served by the bit-parallel matcher
 
 int64_t fwd_items_upper(int64_t N, int64_t S, int64_t uniform_len, bool dense) {
   if (dense) return S * (uniform_len >= 2 ? (uniform_len - 1 + kFwdBand - 1) / kFwdBand : 0);
@@ -41,6 +44,14 @@ FwdLayout fwd_layout(int64_t N, int H, int64_t S, bool transposed_symbols) {
     off = align_up(off + (size_t)N * H * sizeof(int32_t));
     l.kt_off = off;
     off = align_up(off + (size_t)N * H * sizeof(int32_t));
+    l.masks_off = 0;
+    l.mask_words = 0;
+  } else {
+    // occurrence bitmaps of the bit-parallel matcher, sized for the widest symbol it serves
+    // (the sizing function does not know D): H * 2^8 rows of ceil(N / 32) + 1 words
+    l.mask_words = (N + 31) / 32 + 1;
+    l.masks_off = off;
+    off = align_up(off + ((size_t)H << kMaskSymbolBits) * (size_t)l.mask_words * sizeof(uint32_t));
   }
   l.bytes = off;
   return l;
@@ -175,6 +186,10 @@ ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, con
   a.best = reinterpret_cast<unsigned long long*>(ws + l.best_off);
   a.sym_seq_stride = dense ? (int64_t)H * uniform_len : 0;
   a.sym_head_stride = dense ? uniform_len : N;
+  if (D <= kMaskSymbolBits) {
+    a.match_masks = reinterpret_cast<uint32_t*>(ws + l.masks_off);
+    a.mask_words = l.mask_words;
+  }
 
   launch_build_plan(a.plan, st);
   ROSA_CUDA_OK(cudaGetLastError());

@@ -272,6 +272,11 @@ struct FwdArgs {
   int32_t* route_token;           // optional
   unsigned long long* best;       // [N*H] (match length << 32 | local route)
   int64_t sym_seq_stride, sym_head_stride;  // packed symbol addressing
+  // Per-symbol occurrence bitmaps of the key symbols, [H][2^D][mask_words] over the packed
+  // token axis (bit g of row (h, s) set iff key symbol of token g, head h is s); null selects
+  // the run-length matcher.
+  uint32_t* match_masks;
+  int64_t mask_words;
 };
 
 int launch_pack_symbols(const void* q, const void* k, int dtype, int64_t N, int H, int D,

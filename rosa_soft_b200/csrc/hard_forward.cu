@@ -11,6 +11,7 @@
 // across bands with one 64-bit integer atomicMax (order independent, hence exact and
 // deterministic).
 #include "common.cuh"
+#include "bit_match.cuh"
 
 namespace rosa {
 
@@ -225,6 +226,70 @@ __global__ void __launch_bounds__(kMatchThreads)
   }
 }
 
+// ------------------------------------------------- bit-parallel matcher (D <= 8)
+// The matcher itself is bit_match_row (bit_match.cuh).  Here: the occurrence bitmaps of the
+// key symbols over the packed token axis, [H][2^D][mask_words], and the kernel that gives one
+// warp to every (token, head) and writes the row winner without atomics.
+
+// Occurrence bitmaps: one warp per 32 consecutive tokens of one head; the lanes that share a
+// symbol are found with match.any and the lowest of them stores the word.
+__global__ void build_match_masks_kernel(Plan plan, const int32_t* __restrict__ ksym, int64_t N,
+                                         int H, int D, int64_t sym_seq_stride,
+                                         int64_t sym_head_stride, uint32_t* __restrict__ masks,
+                                         int64_t mask_words) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t words = (N + 31) >> 5;
+  if (warp_id >= words * H) return;
+  const int h = (int)(warp_id / words);
+  const int64_t word = warp_id - (int64_t)h * words;
+  const int64_t g = word * 32 + lane;
+  // lanes past the end get distinct out-of-range symbols so that they match nobody
+  unsigned sym = 0x80000000u | (unsigned)lane;
+  if (g < N) {
+    int start = 0, len = 0;
+    const int seq = find_segment(plan, g, &start, &len);
+    if (seq >= 0) {
+      const bool dense = plan.cu_seqlens == nullptr;
+      const int64_t idx = (int64_t)seq * sym_seq_stride + (int64_t)h * sym_head_stride +
+                          (dense ? g - start : g);
+      sym = (unsigned)ksym[idx];
+    }
+  }
+  const unsigned peers = __match_any_sync(0xffffffffu, sym);
+  if (sym < (1u << D) && lane == __ffs(peers) - 1)
+    masks[(((int64_t)h << D) + sym) * mask_words + word] = peers;
+}
+
+constexpr int kBitsWarps = 8;
+
+__global__ void __launch_bounds__(kBitsWarps * 32)
+    hard_match_bits_kernel(Plan plan, const int32_t* __restrict__ qsym,
+                           const uint32_t* __restrict__ masks, int64_t N, int H, int D, int W,
+                           int64_t mask_words, int64_t sym_seq_stride, int64_t sym_head_stride,
+                           unsigned long long* __restrict__ best) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kBitsWarps + (threadIdx.x >> 5);
+  if (row >= N * H) return;
+  // head-major order: neighbouring warps work on neighbouring rows of one head's bitmaps
+  const int h = (int)(row / N);
+  const int64_t g = row - (int64_t)h * N;
+  unsigned long long* out = best + g * H + h;
+  int start = 0, len = 0;
+  const int seq = find_segment(plan, g, &start, &len);
+  const int i = (int)(g - start);
+  if (seq < 0 || i == 0) {
+    if (lane == 0) *out = 0ull;
+    return;
+  }
+  const bool dense = plan.cu_seqlens == nullptr;
+  const int32_t* __restrict__ q = qsym + (int64_t)seq * sym_seq_stride +
+                                  (int64_t)h * sym_head_stride + (dense ? 0 : start);
+  const unsigned long long key =
+      bit_match_row(q, masks + ((int64_t)h << D) * mask_words, mask_words, start, i, W, lane);
+  if (lane == 0) *out = key;
+}
+
 // ------------------------------------------------------------------- gather
 template <typename T>
 __device__ __forceinline__ T from_float(float x);
@@ -339,6 +404,27 @@ int launch_transpose_symbols(const uint32_t* q, const uint32_t* k, int64_t N, in
 }
 
 int launch_hard_match(const FwdArgs& a, int items_upper, cudaStream_t stream) {
+  if (a.match_masks != nullptr) {
+    if (a.N == 0) return 0;
+    {
+      ProfileScope prof("build_match_masks", stream);
+      ROSA_CUDA_OK(cudaMemsetAsync(a.match_masks, 0,
+                                   ((size_t)a.H << a.D) * (size_t)a.mask_words * sizeof(uint32_t),
+                                   stream));
+      const int64_t warps = ((a.N + 31) >> 5) * a.H;
+      build_match_masks_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(
+          a.plan, a.packed_k, a.N, a.H, a.D, a.sym_seq_stride, a.sym_head_stride, a.match_masks,
+          a.mask_words);
+      ROSA_CUDA_OK(cudaGetLastError());
+    }
+    ProfileScope prof("hard_match", stream);
+    const int64_t rows = a.N * a.H;
+    hard_match_bits_kernel<<<(unsigned)((rows + kBitsWarps - 1) / kBitsWarps), kBitsWarps * 32, 0,
+                             stream>>>(a.plan, a.packed_q, a.match_masks, a.N, a.H, a.D, a.W,
+                                       a.mask_words, a.sym_seq_stride, a.sym_head_stride, a.best);
+    ROSA_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
   if (items_upper <= 0) return 0;
   ProfileScope prof("hard_match", stream);
   const int64_t max_len = a.plan.cu_seqlens == nullptr ? a.plan.uniform_len : a.N;
