@@ -150,22 +150,23 @@ ROSA_B200_API int rosa_b200_hard_inference(const uint32_t* query_symbols, const 
  * Chunked update with the per-slot state kept on the GPU: the device form of
  * RosaRuntime::update_packed (reference rosa_soft/csrc/rosa_runtime.cpp:333-482; the
  * automaton step it replaces :103-133; successor payload :455-467; reset :492-498).
- * The caller owns the state and passes it to every call:
- *   key_history     uint8  [slots, num_heads, capacity]          key symbols seen so far
- *   run_state       uint16 [slots, num_heads, capacity]          capped run length per diagonal
+ * The caller owns the state and passes it to every call (capacity a multiple of 32):
+ *   key_masks       uint32 [slots, num_heads, 2^qk_bits, capacity/32]  one occurrence bitmap per
+ *                                                     key symbol: bit p set iff key[p] == symbol
+ *   query_history   uint8  [slots, num_heads, capacity]
  *   payload_history uint8  [slots, num_payload_heads, capacity]
- *   lengths         int32  [slots]                               tokens held per slot
- * A fresh or reset runtime is `lengths` = 0; the other arrays need no initialisation.
- * The chunk is token-major: query/key [chunk_tokens, num_heads], payload
+ *   lengths         int32  [slots]                    tokens held per slot
+ * A fresh or reset runtime is `lengths` = 0 and `key_masks` = 0; the histories need no
+ * initialisation.  The chunk is token-major: query/key [chunk_tokens, num_heads], payload
  * [chunk_tokens, num_payload_heads], `chunk_offsets` int32 [slots + 1] on the device
  * (slot s owns chunk tokens [offsets[s], offsets[s+1]); empty slots allowed).  Symbols are
  * masked to qk_bits / payload_bits (1..8).  For every chunk token and head the call writes
  * the payload symbol that followed the latest-longest match (0 for no match) to `output`
  * and the matched key end position inside the slot's whole history (-1 for no match) to
- * `matched_key_end`, appends the chunk to the histories and advances `lengths`.
+ * `matched_key_end`, appends the chunk to the state and advances `lengths`.
  * `max_length_after` is a host-side upper bound of lengths[s] + chunk length over the slots
- * (it sizes the grid; the host knows it because it chose the chunk).  The result does not
- * depend on how a stream was cut into chunks.  max_suffix_length <= 65535.
+ * (the host knows it because it chose the chunk); it must not exceed `capacity`.  The result
+ * does not depend on how a stream was cut into chunks.
  * A bad `chunk_offsets` or a slot that would outgrow `capacity` leaves the state untouched
  * and is reported through rosa_b200_read_status (ROSA_B200_STATUS_CAPACITY for the latter).
  * Calls that share a state must be ordered on one stream. */
@@ -175,7 +176,7 @@ ROSA_B200_API int rosa_b200_stream_update(
     const uint8_t* query, const uint8_t* key, const uint8_t* payload,
     const int32_t* chunk_offsets, int64_t chunk_tokens, int slots, int num_heads,
     int num_payload_heads, int qk_bits, int payload_bits, int64_t max_suffix_length,
-    uint8_t* key_history, uint16_t* run_state, uint8_t* payload_history, int32_t* lengths,
+    uint32_t* key_masks, uint8_t* query_history, uint8_t* payload_history, int32_t* lengths,
     int64_t capacity, int64_t max_length_after, uint8_t* output, int64_t* matched_key_end,
     void* workspace, size_t workspace_bytes, void* stream);
 

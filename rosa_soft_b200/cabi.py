@@ -242,7 +242,7 @@ def hard_inference(qsym, ksym, payload, cu_seqlens, max_suffix_length, stream=No
 
 
 def stream_update(query, key, payload, chunk_offsets, qk_bits, payload_bits, max_suffix_length,
-                  key_history, run_state, payload_history, lengths, max_length_after, stream=None):
+                  key_masks, query_history, payload_history, lengths, max_length_after, stream=None):
     """One chunked update of the GPU streaming runtime.
 
     query/key uint8 [n, H], payload uint8 [n, Hp], chunk_offsets int32 [slots + 1] (device);
@@ -254,7 +254,7 @@ def stream_update(query, key, payload, chunk_offsets, qk_bits, payload_bits, max
     n, H = query.shape
     Hp = payload.shape[1]
     slots = chunk_offsets.numel() - 1
-    capacity = key_history.shape[-1]
+    capacity = query_history.shape[-1]
     out = torch.empty((n, H), dtype=torch.uint8, device=query.device)
     end = torch.empty((n, H), dtype=torch.int64, device=query.device)
     nbytes = lib.rosa_b200_stream_workspace_bytes(n, H)
@@ -262,7 +262,7 @@ def stream_update(query, key, payload, chunk_offsets, qk_bits, payload_bits, max
     st = stream if stream is not None else torch.cuda.current_stream(query.device).cuda_stream
     check(lib.rosa_b200_stream_update(_ptr(query), _ptr(key), _ptr(payload), _ptr(chunk_offsets), n,
                                       slots, H, Hp, int(qk_bits), int(payload_bits),
-                                      int(max_suffix_length), _ptr(key_history), _ptr(run_state),
+                                      int(max_suffix_length), _ptr(key_masks), _ptr(query_history),
                                       _ptr(payload_history), _ptr(lengths), capacity,
                                       int(max_length_after), _ptr(out), _ptr(end), _ptr(ws), nbytes,
                                       ctypes.c_void_p(st)))

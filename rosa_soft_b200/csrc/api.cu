@@ -270,7 +270,7 @@ ROSA_B200_API int rosa_b200_stream_update(
     const uint8_t* query, const uint8_t* key, const uint8_t* payload,
     const int32_t* chunk_offsets, int64_t chunk_tokens, int slots, int num_heads,
     int num_payload_heads, int qk_bits, int payload_bits, int64_t max_suffix_length,
-    uint8_t* key_history, uint16_t* run_state, uint8_t* payload_history, int32_t* lengths,
+    uint32_t* key_masks, uint8_t* query_history, uint8_t* payload_history, int32_t* lengths,
     int64_t capacity, int64_t max_length_after, uint8_t* output, int64_t* matched_key_end,
     void* workspace, size_t workspace_bytes, void* stream) {
   ROSA_REQUIRE(slots >= 1, "slot count must be >= 1");
@@ -279,34 +279,32 @@ ROSA_B200_API int rosa_b200_stream_update(
                "num_heads must be divisible by num_payload_heads");
   ROSA_REQUIRE(qk_bits >= 1 && qk_bits <= 8, "qk_bits must be in [1, 8]");
   ROSA_REQUIRE(payload_bits >= 1 && payload_bits <= 8, "payload_bits must be in [1, 8]");
-  ROSA_REQUIRE(max_suffix_length >= 1 && max_suffix_length <= 65535,
-               "max_suffix_length must be in [1, 65535] for the streaming runtime");
+  ROSA_REQUIRE(max_suffix_length >= 1, "max_suffix_length must be >= 1");
   ROSA_REQUIRE(chunk_tokens >= 0, "chunk token count must be non-negative");
-  ROSA_REQUIRE(capacity >= 1 && capacity <= std::numeric_limits<int32_t>::max(),
-               "history capacity must be in [1, 2^31)");
+  ROSA_REQUIRE(capacity >= 32 && capacity % 32 == 0 &&
+                   capacity <= std::numeric_limits<int32_t>::max() - 31,
+               "history capacity must be a multiple of 32 in [32, 2^31)");
   ROSA_REQUIRE(max_length_after >= 0 && max_length_after <= capacity,
                "max_length_after exceeds the history capacity");
   ROSA_REQUIRE(chunk_tokens * (int64_t)num_heads <= std::numeric_limits<int32_t>::max(),
                "chunk_tokens * num_heads exceeds the int32 range");
-  ROSA_REQUIRE(chunk_offsets && key_history && run_state && payload_history && lengths && workspace,
+  ROSA_REQUIRE(chunk_offsets && key_masks && query_history && payload_history && lengths && workspace,
                "null pointer argument");
   ROSA_REQUIRE(chunk_tokens == 0 || (query && key && payload && output && matched_key_end),
                "null pointer argument");
   const size_t need = rosa_b200_stream_workspace_bytes(chunk_tokens, num_heads);
   ROSA_REQUIRE(workspace_bytes >= need, "workspace too small: need %zu bytes, got %zu", need,
                workspace_bytes);
-  const int64_t bands = std::max<int64_t>(1, (max_length_after + 1022) / 1024);
-  ROSA_REQUIRE(bands * slots * (int64_t)num_heads <= std::numeric_limits<int32_t>::max(),
-               "grid too large: slots * heads * history length");
   StreamArgs a{};
   a.query = query; a.key = key; a.payload = payload;
   a.offsets = chunk_offsets;
   a.chunk_tokens = chunk_tokens;
   a.slots = slots; a.H = num_heads; a.Hp = num_payload_heads;
+  a.qk_bits = qk_bits;
   a.qk_mask = (1 << qk_bits) - 1;
   a.payload_mask = (1 << payload_bits) - 1;
-  a.W = (int)max_suffix_length;
-  a.key_history = key_history; a.run_state = run_state; a.payload_history = payload_history;
+  a.W = (int)std::min<int64_t>(max_suffix_length, capacity);
+  a.key_masks = key_masks; a.query_history = query_history; a.payload_history = payload_history;
   a.lengths = lengths;
   a.capacity = capacity;
   a.max_length_after = max_length_after;

@@ -299,9 +299,9 @@ struct StreamArgs {
   const uint8_t* payload;      // [chunk_tokens, Hp]
   const int32_t* offsets;      // [slots + 1] chunk offsets per slot
   int64_t chunk_tokens;
-  int slots, H, Hp, qk_mask, payload_mask, W;
-  uint8_t* key_history;        // [slots, H, capacity]
-  uint16_t* run_state;         // [slots, H, capacity] capped run length per diagonal
+  int slots, H, Hp, qk_bits, qk_mask, payload_mask, W;
+  uint32_t* key_masks;         // [slots, H, 2^qk_bits, capacity / 32] occurrence bitmaps
+  uint8_t* query_history;      // [slots, H, capacity]
   uint8_t* payload_history;    // [slots, Hp, capacity]
   int32_t* lengths;            // [slots] tokens held per slot, advanced by the call
   int64_t capacity;

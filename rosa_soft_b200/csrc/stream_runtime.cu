@@ -3,22 +3,20 @@
 // automaton step :103-133, successor payload :455-467, slot-count fixing :531-556).
 //
 // The reference keeps one finite-horizon suffix automaton per (slot, head) on the host.  Here
-// the state of a (slot, head) is its key-symbol history plus one capped run length per
-// diagonal: run[delta] = number of trailing positions p <= last with q[p] == k[p - delta],
-// capped at the horizon.  A new query row i extends every diagonal by one cell, so a chunk of n
-// tokens on a history of L tokens costs n * (L + n) symbol compares, independent of how the
-// stream was chunked before, and the result equals a one-shot pass over the whole stream.
+// the state of a (slot, head) is the query history plus one occurrence bitmap per key symbol
+// (bit p of bitmap s set iff the key symbol at position p is s; symbols have at most 8 bits).
+// A new row is resolved by the bit-parallel matcher of bit_match.cuh: per 32 key positions it
+// costs as many AND steps as the longest match in that word is long, so a chunk of n tokens on
+// a history of L tokens costs about n * (L / 32) * (a few levels) word operations, and the
+// result equals a one-shot pass over the whole stream however it was chunked.
 #include "common.cuh"
+#include "bit_match.cuh"
 
 namespace rosa {
 
 namespace {
 
-constexpr int kStreamThreads = 256;
-constexpr int kStreamPer = 4;                                  // diagonals per thread
-constexpr int kStreamBand = kStreamThreads * kStreamPer;       // diagonals per CTA
-constexpr int kStreamRows = 32;                                // rows per staged block
-constexpr int kStreamWin = kStreamBand + kStreamRows;
+constexpr int kStreamWarps = 8;   // rows per CTA of the matcher
 
 // slot containing chunk token `token`: the last s with offsets[s] <= token
 __device__ __forceinline__ int stream_slot(const int32_t* __restrict__ offsets, int slots,
@@ -56,15 +54,17 @@ __global__ void stream_prepare_kernel(const int32_t* __restrict__ offsets, int s
   }
 }
 
-// Appends the chunk's key and payload symbols to the histories and clears the winners.
-__global__ void stream_append_kernel(const uint8_t* __restrict__ key,
+// Appends the chunk to the state: query and payload symbols to their histories, every key
+// symbol as one bit of its occurrence bitmap (atomic OR: several tokens of a chunk share a word).
+__global__ void stream_append_kernel(const uint8_t* __restrict__ query,
+                                     const uint8_t* __restrict__ key,
                                      const uint8_t* __restrict__ payload,
                                      const int32_t* __restrict__ offsets, int slots,
-                                     int64_t chunk_tokens, int H, int Hp, int qk_mask,
+                                     int64_t chunk_tokens, int H, int Hp, int qk_bits, int qk_mask,
                                      int payload_mask, const int32_t* __restrict__ lengths,
-                                     int64_t capacity, uint8_t* __restrict__ key_history,
+                                     int64_t capacity, uint32_t* __restrict__ key_masks,
+                                     uint8_t* __restrict__ query_history,
                                      uint8_t* __restrict__ payload_history,
-                                     unsigned long long* __restrict__ best,
                                      const int32_t* __restrict__ status) {
   if (status[0] != 0) return;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -75,8 +75,10 @@ __global__ void stream_append_kernel(const uint8_t* __restrict__ key,
   const int s = stream_slot(offsets, slots, token);
   const int64_t pos = (int64_t)lengths[s] + (token - offsets[s]);
   if (hh < H) {
-    key_history[((int64_t)s * H + hh) * capacity + pos] = key[token * H + hh] & qk_mask;
-    best[token * H + hh] = 0ull;
+    const int64_t sh = (int64_t)s * H + hh;
+    query_history[sh * capacity + pos] = query[token * H + hh] & qk_mask;
+    const int sym = key[token * H + hh] & qk_mask;
+    atomicOr(key_masks + ((sh << qk_bits) + sym) * (capacity >> 5) + (pos >> 5), 1u << (pos & 31));
   } else {
     const int hp = hh - H;
     payload_history[((int64_t)s * Hp + hp) * capacity + pos] =
@@ -84,114 +86,31 @@ __global__ void stream_append_kernel(const uint8_t* __restrict__ key,
   }
 }
 
-// Candidate of a cell.  Narrow: run << 21 | route in 32 bits (horizon < 2048, history < 2^21).
-template <bool kWide>
-struct StreamKey;
-template <>
-struct StreamKey<false> {
-  using type = unsigned;
-  static __device__ __forceinline__ unsigned make(int run, int route) {
-    return ((unsigned)run << 21) + (unsigned)route;
-  }
-  static __device__ __forceinline__ unsigned warp_max(unsigned v) {
-    return __reduce_max_sync(0xffffffffu, v);
-  }
-  static __device__ __forceinline__ unsigned long long widen(unsigned v) {
-    return ((unsigned long long)(v >> 21) << 32) | (unsigned long long)(v & 0x1FFFFFu);
-  }
-};
-template <>
-struct StreamKey<true> {
-  using type = unsigned long long;
-  static __device__ __forceinline__ unsigned long long make(int run, int route) {
-    return ((unsigned long long)(unsigned)run << 32) | (unsigned)route;
-  }
-  static __device__ __forceinline__ unsigned long long warp_max(unsigned long long v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
-      v = other > v ? other : v;
-    }
-    return v;
-  }
-  static __device__ __forceinline__ unsigned long long widen(unsigned long long v) { return v; }
-};
-
-// One CTA = kStreamBand diagonals of one (slot, head); rows are the chunk's new positions.
-template <bool kWide>
-__global__ void __launch_bounds__(kStreamThreads)
-    stream_match_kernel(const uint8_t* __restrict__ query, const int32_t* __restrict__ offsets,
-                        int slots, int H, int qk_mask, int W,
-                        const int32_t* __restrict__ lengths, int64_t capacity,
-                        const uint8_t* __restrict__ key_history, uint16_t* __restrict__ run_state,
+// One warp per (chunk token, head), head-major so that neighbouring warps read the same
+// bitmaps.  Writes (match length << 32 | successor position) or 0.
+__global__ void __launch_bounds__(kStreamWarps * 32)
+    stream_match_kernel(const int32_t* __restrict__ offsets, int slots, int64_t chunk_tokens,
+                        int H, int qk_bits, int W, const int32_t* __restrict__ lengths,
+                        int64_t capacity, const uint32_t* __restrict__ key_masks,
+                        const uint8_t* __restrict__ query_history,
                         unsigned long long* __restrict__ best,
                         const int32_t* __restrict__ status) {
-  using KeyT = typename StreamKey<kWide>::type;
-  __shared__ int s_k[kStreamWin];
-  __shared__ int s_q[kStreamRows];
-  __shared__ KeyT s_best[kStreamRows];
   if (status[0] != 0) return;
-  // heads fastest, then slots, then bands: neighbouring CTAs carry the same amount of work
-  const int h = blockIdx.x % H;
-  const int s = (blockIdx.x / H) % slots;
-  const int band = blockIdx.x / (H * slots);
-  const int L = lengths[s];
-  const int n = offsets[s + 1] - offsets[s];
-  const int Ln = L + n;
-  const int dmin = 1 + band * kStreamBand, dmax = dmin + kStreamBand - 1;
-  if (n == 0 || dmin > Ln - 1) return;
-  const int tid = threadIdx.x, lane = tid & 31;
-  const uint8_t* __restrict__ kh = key_history + ((int64_t)s * H + h) * capacity;
-  uint16_t* __restrict__ rs = run_state + ((int64_t)s * H + h) * capacity;
-  const uint8_t* __restrict__ qc = query + (int64_t)offsets[s] * H + h;
-
-  int run[kStreamPer];
-#pragma unroll
-  for (int u = 0; u < kStreamPer; ++u) {
-    const int delta = dmin + tid + u * kStreamThreads;
-    run[u] = delta <= L - 1 ? (int)rs[delta] : 0;   // diagonals that had a cell before this chunk
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kStreamWarps + (threadIdx.x >> 5);
+  if (row >= chunk_tokens * H) return;
+  const int h = (int)(row / chunk_tokens);
+  const int64_t token = row - (int64_t)h * chunk_tokens;
+  const int s = stream_slot(offsets, slots, token);
+  const int i = lengths[s] + (int)(token - offsets[s]);    // position of the row in its stream
+  unsigned long long key = 0ull;
+  if (i > 0) {
+    const int64_t sh = (int64_t)s * H + h;
+    key = bit_match_row(query_history + sh * capacity,
+                        key_masks + (sh << qk_bits) * (capacity >> 5), capacity >> 5, 0, i, W,
+                        lane);
   }
-
-  for (int i0 = max(L, dmin); i0 < Ln; i0 = (i0 / kStreamRows + 1) * kStreamRows) {
-    const int i1 = min((i0 / kStreamRows + 1) * kStreamRows - 1, Ln - 1);
-    const int nrows = i1 - i0 + 1;
-    const int jwin0 = i0 - dmax;                    // key position of window index 0
-    __syncthreads();
-    for (int c = tid; c < nrows + kStreamBand - 1; c += kStreamThreads) {
-      const int j = jwin0 + c;
-      s_k[c] = (j >= 0 && j < Ln) ? (int)kh[j] : 0;
-    }
-    if (tid < nrows) {
-      s_q[tid] = (int)(qc[(int64_t)(i0 + tid - L) * H] & qk_mask);
-      s_best[tid] = 0;
-    }
-    __syncthreads();
-    const int cmin = jwin0 < 0 ? -jwin0 : 0;        // window indices before the stream's start
-    for (int r = 0; r < nrows; ++r) {
-      const int qi = s_q[r];
-      KeyT top = 0;
-#pragma unroll
-      for (int u = 0; u < kStreamPer; ++u) {
-        const int c = kStreamBand - 1 - tid - u * kStreamThreads + r;
-        const bool eq = s_k[c] == qi && c >= cmin;
-        const int l = eq ? min(run[u] + 1, W) : 0;
-        run[u] = l;
-        const KeyT key = StreamKey<kWide>::make(l, jwin0 + c + 1);   // route = key position + 1
-        if (eq && key > top) top = key;
-      }
-      const KeyT wtop = StreamKey<kWide>::warp_max(top);
-      if (lane == 0 && wtop > 0) atomicMax(s_best + r, wtop);
-    }
-    __syncthreads();
-    if (tid < nrows && s_best[tid] > 0)
-      atomicMax(best + ((int64_t)(offsets[s] + i0 + tid - L) * H + h),
-                StreamKey<kWide>::widen(s_best[tid]));
-  }
-#pragma unroll
-  for (int u = 0; u < kStreamPer; ++u) {
-    const int delta = dmin + tid + u * kStreamThreads;
-    if (delta <= Ln - 1) rs[delta] = (uint16_t)run[u];
-  }
+  if (lane == 0) best[token * H + h] = key;
 }
 
 __global__ void stream_finish_kernel(const unsigned long long* __restrict__ best,
@@ -236,22 +155,18 @@ int launch_stream_update(const StreamArgs& a, cudaStream_t stream) {
     ProfileScope prof("stream_append", stream);
     const int64_t total = a.chunk_tokens * (a.H + a.Hp);
     stream_append_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(
-        a.key, a.payload, a.offsets, a.slots, a.chunk_tokens, a.H, a.Hp, a.qk_mask, a.payload_mask,
-        a.lengths, a.capacity, a.key_history, a.payload_history, a.best, a.status);
+        a.query, a.key, a.payload, a.offsets, a.slots, a.chunk_tokens, a.H, a.Hp, a.qk_bits,
+        a.qk_mask, a.payload_mask, a.lengths, a.capacity, a.key_masks, a.query_history,
+        a.payload_history, a.status);
     ROSA_CUDA_OK(cudaGetLastError());
   }
   {
     ProfileScope prof("stream_match", stream);
-    const int64_t bands = std::max<int64_t>(1, (a.max_length_after - 1 + kStreamBand - 1) / kStreamBand);
-    const int64_t grid = bands * a.slots * a.H;
-    if (a.W < 2048 && a.capacity < (1 << 21))
-      stream_match_kernel<false><<<(unsigned)grid, kStreamThreads, 0, stream>>>(
-          a.query, a.offsets, a.slots, a.H, a.qk_mask, a.W, a.lengths, a.capacity, a.key_history,
-          a.run_state, a.best, a.status);
-    else
-      stream_match_kernel<true><<<(unsigned)grid, kStreamThreads, 0, stream>>>(
-          a.query, a.offsets, a.slots, a.H, a.qk_mask, a.W, a.lengths, a.capacity, a.key_history,
-          a.run_state, a.best, a.status);
+    const int64_t rows = a.chunk_tokens * a.H;
+    stream_match_kernel<<<(unsigned)((rows + kStreamWarps - 1) / kStreamWarps), kStreamWarps * 32,
+                          0, stream>>>(a.offsets, a.slots, a.chunk_tokens, a.H, a.qk_bits, a.W,
+                                       a.lengths, a.capacity, a.key_masks, a.query_history, a.best,
+                                       a.status);
     ROSA_CUDA_OK(cudaGetLastError());
   }
   {

@@ -5,10 +5,11 @@ rosa_soft/csrc/rosa_runtime.cpp:216-556) for the 1..8-bit packed deployment subs
 constructor, properties, ``update`` / ``update_packed`` signatures, slot fixing, ``sequence_ids``
 checks, ``reset`` / ``close`` life cycle and error texts.  The difference is where the state
 lives: the reference stages every update to the CPU, steps one suffix automaton per
-(slot, head) there and copies the result back (runtime.py:728-773); this class keeps the key
-and payload histories and one capped run length per diagonal in HBM and updates them with
-``rosa_b200_stream_update``, so a chunk never leaves the device and the call only enqueues
-work on a CUDA stream.  Results are identical to a one-shot pass whatever the chunking.
+(slot, head) there and copies the result back (runtime.py:728-773); this class keeps the query
+and payload histories and one occurrence bitmap per key symbol in HBM and updates them with
+``rosa_b200_stream_update`` (a bit-parallel matcher), so a chunk never leaves the device and
+the call only enqueues work on a CUDA stream.  Results are identical to a one-shot pass
+whatever the chunking.
 """
 from __future__ import annotations
 
@@ -21,7 +22,6 @@ from torch import Tensor
 from . import cabi
 
 _MIN_CAPACITY = 256
-_MAX_HORIZON = 65535
 
 
 def _as_index(name: str, value) -> int:
@@ -115,8 +115,8 @@ class RosaRuntime:
             raise ValueError("num_heads and num_payload_heads must be positive")
         if self._num_heads % self._num_payload_heads != 0:
             raise ValueError("num_heads must be divisible by num_payload_heads")
-        if not 1 <= self._max_suffix_length <= _MAX_HORIZON:
-            raise ValueError(f"max_suffix_length must be in [1, {_MAX_HORIZON}]")
+        if self._max_suffix_length < 1:
+            raise ValueError("max_suffix_length must be >= 1")
         cabi.load()  # fail now, not at the first update, when the CUDA library is missing
         self._state = "OPEN"
         self._clear()
@@ -126,9 +126,9 @@ class RosaRuntime:
         self._slots = -1
         self._capacity = 0
         self._lengths_host: list = []
-        self._key_history: Optional[Tensor] = None
-        self._run_state: Optional[Tensor] = None
-        self._payload_history: Optional[Tensor] = None
+        self._key_masks: Optional[Tensor] = None       # [slots, H, 2^qk_bits, capacity / 32]
+        self._query_history: Optional[Tensor] = None   # [slots, H, capacity]
+        self._payload_history: Optional[Tensor] = None  # [slots, Hp, capacity]
         self._lengths: Optional[Tensor] = None
         self._sequence_ids: Optional[Tuple[int, ...]] = None
         self._ids_fixed = False
@@ -184,7 +184,8 @@ class RosaRuntime:
 
     def memory_stats(self) -> Dict[str, int]:
         """Counts of what is held.  ``states`` / ``edges`` are zero: there is no automaton; the
-        matcher's state is one run length per key position (reference runtime.py:557-576)."""
+        matcher's state is one occurrence bit per key position and symbol
+        (reference runtime.py:557-576)."""
         self._require_open()
         tokens = sum(self._lengths_host)
         slots = max(self._slots, 0)
@@ -194,7 +195,8 @@ class RosaRuntime:
             "payload_symbols": tokens * self._num_payload_heads,
             "automata": slots * self._num_heads,
             "sequences": slots,
-            "logical_bytes": tokens * (3 * self._num_heads + self._num_payload_heads),
+            "logical_bytes": tokens * (self._num_heads * (1 + (1 << self._qk_bits) // 8)
+                                       + self._num_payload_heads),
             "capacity_tokens": self._capacity,
         }
 
@@ -213,8 +215,8 @@ class RosaRuntime:
         state: Dict[str, Any] = {"config": config, "lengths": list(self._lengths_host),
                                  "sequence_ids": self._sequence_ids, "ids_fixed": self._ids_fixed}
         if self._slots > 0:
-            state["key_history"] = self._key_history[..., :used].clone()
-            state["run_state"] = self._run_state[..., :used].clone()
+            state["key_masks"] = self._key_masks[..., :(used + 31) // 32].clone()
+            state["query_history"] = self._query_history[..., :used].clone()
             state["payload_history"] = self._payload_history[..., :used].clone()
         return state
 
@@ -230,16 +232,16 @@ class RosaRuntime:
         self._ids_fixed = bool(state_dict.get("ids_fixed", False))
         if not lengths:
             return
-        key_history = state_dict["key_history"]
-        if not key_history.is_cuda:
+        query_history = state_dict["query_history"]
+        if not query_history.is_cuda:
             raise ValueError("state_dict tensors must be CUDA tensors")
-        self._device = key_history.device
+        self._device = query_history.device
         self._slots = len(lengths)
         self._lengths_host = lengths
         self._grow(max(lengths))
-        used = key_history.shape[-1]
-        self._key_history[..., :used] = key_history
-        self._run_state[..., :used] = state_dict["run_state"]
+        used = query_history.shape[-1]
+        self._key_masks[..., :(used + 31) // 32] = state_dict["key_masks"]
+        self._query_history[..., :used] = query_history
         self._payload_history[..., :used] = state_dict["payload_history"]
         self._lengths.copy_(torch.tensor(lengths, dtype=torch.int32))
 
@@ -251,19 +253,20 @@ class RosaRuntime:
         capacity = max(_MIN_CAPACITY, self._capacity)
         while capacity < needed:
             capacity *= 2
-        shape_k = (self._slots, self._num_heads, capacity)
+        shape_m = (self._slots, self._num_heads, 1 << self._qk_bits, capacity // 32)
+        shape_q = (self._slots, self._num_heads, capacity)
         shape_p = (self._slots, self._num_payload_heads, capacity)
-        key_history = torch.empty(shape_k, dtype=torch.uint8, device=self._device)
-        run_state = torch.empty(shape_k, dtype=torch.int16, device=self._device)
+        key_masks = torch.zeros(shape_m, dtype=torch.int32, device=self._device)
+        query_history = torch.empty(shape_q, dtype=torch.uint8, device=self._device)
         payload_history = torch.empty(shape_p, dtype=torch.uint8, device=self._device)
         if self._capacity:
-            key_history[..., :self._capacity] = self._key_history
-            run_state[..., :self._capacity] = self._run_state
+            key_masks[..., :self._capacity // 32] = self._key_masks
+            query_history[..., :self._capacity] = self._query_history
             payload_history[..., :self._capacity] = self._payload_history
         else:
             self._lengths = torch.zeros(self._slots, dtype=torch.int32, device=self._device)
-        self._key_history, self._run_state, self._payload_history = (
-            key_history, run_state, payload_history)
+        self._key_masks, self._query_history, self._payload_history = (
+            key_masks, query_history, payload_history)
         self._capacity = capacity
 
     def _check_sequence_ids(self, sequence_ids: Optional[Tuple[int, ...]]) -> None:
@@ -390,7 +393,7 @@ class RosaRuntime:
             dev_offsets = torch.tensor(offsets, dtype=torch.int32).to(device, non_blocking=True)
             packed, end, workspace = cabi.stream_update(
                 flat_q, flat_k, flat_p, dev_offsets, self.qk_bits, self.payload_bits,
-                self.max_suffix_length, self._key_history, self._run_state, self._payload_history,
+                self.max_suffix_length, self._key_masks, self._query_history, self._payload_history,
                 self._lengths, max(after), stream=run_on.cuda_stream)
             self._lengths_host = after
             if dense:

@@ -70,8 +70,8 @@ def test_streaming_runtime_update_replays_from_a_cuda_graph():
     q = rng.integers(0, 1 << bits, size=(S, steps, H), dtype=np.uint8)
     k = np.where(rng.random((S, steps, H)) < 0.7, q, rng.integers(0, 1 << bits, size=(S, steps, H))).astype(np.uint8)
     p = rng.integers(0, 256, size=(S, steps, Hp), dtype=np.uint8)
-    kh = torch.zeros((S, H, cap), dtype=torch.uint8, device=DEV)
-    run = torch.zeros((S, H, cap), dtype=torch.int16, device=DEV)
+    kh = torch.zeros((S, H, 1 << bits, cap // 32), dtype=torch.int32, device=DEV)
+    run = torch.zeros((S, H, cap), dtype=torch.uint8, device=DEV)
     ph = torch.zeros((S, Hp, cap), dtype=torch.uint8, device=DEV)
     lengths = torch.zeros(S, dtype=torch.int32, device=DEV)
     off = torch.arange(S + 1, dtype=torch.int32, device=DEV)

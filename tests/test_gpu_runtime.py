@@ -145,8 +145,8 @@ def test_token_by_token_decode_after_prefill():
 
 
 def test_wide_keys_for_long_horizons():
-    """Horizons of 2048 and more take the 64-bit candidate path; a constant stream makes the run
-    length actually exceed 2047."""
+    """A horizon of thousands of tokens on a nearly constant stream: the match lengths reach the
+    horizon, the level loop of the bit matcher runs thousands of steps per word."""
     from rosa_soft_b200 import RosaRuntime
     H, Hp, W, L = 2, 1, 3000, 3500
     q = np.zeros((L, H), dtype=np.uint8)
@@ -236,23 +236,27 @@ def test_side_stream_and_async_handle():
 
 def test_c_abi_reports_capacity_and_bad_offsets_without_touching_state():
     from rosa_soft_b200 import cabi
-    S, H, Hp, cap = 2, 2, 1, 64
-    kh = torch.zeros((S, H, cap), dtype=torch.uint8, device=DEV)
-    rs = torch.zeros((S, H, cap), dtype=torch.int16, device=DEV)
+    S, H, Hp, cap, bits = 2, 2, 1, 64, 1
+    km = torch.zeros((S, H, 1 << bits, cap // 32), dtype=torch.int32, device=DEV)
+    qh = torch.zeros((S, H, cap), dtype=torch.uint8, device=DEV)
     ph = torch.zeros((S, Hp, cap), dtype=torch.uint8, device=DEV)
     lengths = torch.tensor([60, 3], dtype=torch.int32, device=DEV)
     n = 10
     q = torch.ones((n, H), dtype=torch.uint8, device=DEV)
     p = torch.ones((n, Hp), dtype=torch.uint8, device=DEV)
     off = torch.tensor([0, 5, 10], dtype=torch.int32, device=DEV)      # slot 0 would reach 65 > 64
-    _, _, ws = cabi.stream_update(q, q, p, off, 1, 1, 4, kh, rs, ph, lengths, 64)
+    _, _, ws = cabi.stream_update(q, q, p, off, bits, 1, 4, km, qh, ph, lengths, 64)
     assert cabi.read_status(ws) == 4
-    assert lengths.tolist() == [60, 3] and int(kh.sum()) == 0
+    assert lengths.tolist() == [60, 3] and int(km.ne(0).sum()) == 0 and int(qh.sum()) == 0
     off = torch.tensor([0, 3, 2], dtype=torch.int32, device=DEV)
-    _, _, ws = cabi.stream_update(q, q, p, off, 1, 1, 4, kh, rs, ph, lengths, 64)
+    _, _, ws = cabi.stream_update(q, q, p, off, bits, 1, 4, km, qh, ph, lengths, 64)
     assert cabi.read_status(ws) in (2, 3)
     assert lengths.tolist() == [60, 3]
     off = torch.tensor([0, 4, 10], dtype=torch.int32, device=DEV)
-    _, _, ws = cabi.stream_update(q, q, p, off, 1, 1, 4, kh, rs, ph, lengths, 64)
+    _, _, ws = cabi.stream_update(q, q, p, off, bits, 1, 4, km, qh, ph, lengths, 64)
     assert cabi.read_status(ws) == 0
     assert lengths.tolist() == [64, 9]
+    # the appended key symbols (all 1) are bits 60..63 of slot 0 and 3..8 of slot 1 in bitmap 1
+    words = km.view(S, H, 2, cap // 32).cpu().numpy().astype("uint32")
+    assert int(words[0, 0, 1, 1]) == 0xF0000000 and int(words[1, 1, 1, 0]) == 0x1F8
+    assert int(words[:, :, 0].sum()) == 0
