@@ -24,6 +24,12 @@ namespace rosa {
 // positions start .. start + i - 1 (i >= 1).  Returns (match length << 32 | route) with route
 // the winning key position + 1 relative to the sequence start, or 0 for no match; every lane
 // returns the same value.  All 32 lanes must call.
+//
+// A lane holds kBitSpan words at once (the warp covers 32 * 32 * kBitSpan key positions per
+// pass, newest first) and advances all of them level by level, so the loads of one level are
+// in flight together instead of one dependent load chain per word.
+constexpr int kBitSpan = 8;
+
 template <typename Sym>
 __device__ __forceinline__ unsigned long long bit_match_row(const Sym* __restrict__ q,
                                                             const uint32_t* __restrict__ e,
@@ -35,45 +41,61 @@ __device__ __forceinline__ unsigned long long bit_match_row(const Sym* __restric
   // every warp-wide primitive below is executed by all 32 lanes, never under a per-lane
   // condition
   const int sym_first = __shfl_sync(0xffffffffu, q_first, 0);
+  const uint32_t* __restrict__ first_row = e + (int64_t)sym_first * mask_words;
   int best_len = 0, best_route = 0;
 
-  for (int wb = w_hi; wb >= w_lo; wb -= 32) {             // newest positions first
-    const int w = wb - lane;
-    const bool in = w >= w_lo;
-    uint32_t cur = in ? e[(int64_t)sym_first * mask_words + w] : 0u;
-    if (w == w_hi) cur &= 0xffffffffu >> (31 - (g_hi & 31));
-    if (w == w_lo) cur &= 0xffffffffu << (g_lo & 31);
-    int length = cur ? 1 : 0;
-    bool alive = cur != 0u;
+  for (int wtop = w_hi; wtop >= w_lo; wtop -= 32 * kBitSpan) {   // newest positions first
+    uint32_t cur[kBitSpan];
+    int length[kBitSpan];
+    unsigned alive = 0u;                                  // bit c: word c can still extend
+#pragma unroll
+    for (int c = 0; c < kBitSpan; ++c) {
+      const int w = wtop - 32 * c - lane;
+      uint32_t bits = w >= w_lo ? first_row[w] : 0u;
+      if (w == w_hi) bits &= 0xffffffffu >> (31 - (g_hi & 31));
+      if (w == w_lo) bits &= 0xffffffffu << (g_lo & 31);
+      cur[c] = bits;
+      length[c] = bits ? 1 : 0;
+      alive |= bits ? 1u << c : 0u;
+    }
     int qv = q_first;
-    for (int lev = 1; lev < W && __any_sync(0xffffffffu, alive); ++lev) {
+    for (int lev = 1; lev < W && __any_sync(0xffffffffu, alive != 0u); ++lev) {
       if ((lev & 31) == 0) qv = lev + lane <= i ? (int)q[i - lev - lane] : 0;
       const int sym = __shfl_sync(0xffffffffu, qv, lev & 31);
-      if (alive) {
-        // bit g of the shifted bitmap is bit g - lev of E[sym]; it may only extend a match
-        // that still has a predecessor inside the sequence: g - lev >= start
-        const int sh = lev & 31, hi_w = w - (lev >> 5);
-        const uint32_t* row = e + (int64_t)sym * mask_words;
-        const uint32_t hi = hi_w >= w_lo ? row[hi_w] : 0u;
-        const uint32_t lo = (sh != 0 && hi_w - 1 >= w_lo) ? row[hi_w - 1] : 0u;
-        uint32_t m = __funnelshift_l(lo, hi, sh);
-        const int lim = start + lev - 32 * w;             // bits below lim have no predecessor
-        if (lim > 0) m = lim >= 32 ? 0u : m & (0xffffffffu << lim);
-        const uint32_t next = cur & m;
-        if (next != 0u) {
-          cur = next;
-          length = lev + 1;
-        } else {
-          alive = false;
+      const uint32_t* __restrict__ row = e + (int64_t)sym * mask_words;
+      const int sh = lev & 31;
+#pragma unroll
+      for (int c = 0; c < kBitSpan; ++c) {
+        if (alive >> c & 1u) {
+          // bit g of the shifted bitmap is bit g - lev of E[sym]; it may only extend a match
+          // that still has a predecessor inside the sequence: g - lev >= start
+          const int w = wtop - 32 * c - lane;
+          const int hi_w = w - (lev >> 5);
+          const uint32_t hi = hi_w >= w_lo ? row[hi_w] : 0u;
+          const uint32_t lo = (sh != 0 && hi_w - 1 >= w_lo) ? row[hi_w - 1] : 0u;
+          uint32_t m = __funnelshift_l(lo, hi, sh);
+          const int lim = start + lev - 32 * w;           // bits below lim have no predecessor
+          if (lim > 0) m = lim >= 32 ? 0u : m & (0xffffffffu << lim);
+          const uint32_t next = cur[c] & m;
+          if (next != 0u) {
+            cur[c] = next;
+            length[c] = lev + 1;
+          } else {
+            alive &= ~(1u << c);
+          }
         }
       }
     }
-    if (length > 0) {
-      const int pos = 32 * w + 31 - __clz(cur);           // latest position of the longest match
-      const int route = pos - start + 1;
-      if (length > best_len || (length == best_len && route > best_route)) {
-        best_len = length;
-        best_route = route;
+#pragma unroll
+    for (int c = 0; c < kBitSpan; ++c) {
+      if (length[c] > 0) {
+        const int w = wtop - 32 * c - lane;
+        const int pos = 32 * w + 31 - __clz(cur[c]);      // latest position of the longest match
+        const int route = pos - start + 1;
+        if (length[c] > best_len || (length[c] == best_len && route > best_route)) {
+          best_len = length[c];
+          best_route = route;
+        }
       }
     }
     // newer positions were examined first: nothing older can beat a match at the horizon
