@@ -28,7 +28,10 @@ namespace rosa {
 // A lane holds kBitSpan words at once (the warp covers 32 * 32 * kBitSpan key positions per
 // pass, newest first) and advances all of them level by level, so the loads of one level are
 // in flight together instead of one dependent load chain per word.
-constexpr int kBitSpan = 8;
+#ifndef ROSA_BIT_SPAN
+#define ROSA_BIT_SPAN 1
+#endif
+constexpr int kBitSpan = ROSA_BIT_SPAN;
 
 template <typename Sym>
 __device__ __forceinline__ unsigned long long bit_match_row(const Sym* __restrict__ q,
