@@ -21,23 +21,29 @@ namespace rosa {
 // One warp evaluates one query row.  `q[p]` is the query symbol p positions after the
 // sequence start (p <= i readable), `e` the bitmaps of this head, row s at e + s * mask_words,
 // over an axis on which the sequence starts at bit `start`; the candidates of the row are key
-// positions start .. start + i - 1 (i >= 1).  Returns (match length << 32 | route) with route
-// the winning key position + 1 relative to the sequence start, or 0 for no match; every lane
-// returns the same value.  All 32 lanes must call.
+// positions start .. start + i - 1 (i >= 1).  `queue` is kBitQueue entries of shared memory
+// private to the calling warp.  Returns (match length << 32 | route) with route the winning key
+// position + 1 relative to the sequence start, or 0 for no match; every lane returns the same
+// value.  All 32 lanes must call.
 //
-// A lane holds kBitSpan words at once (the warp covers 32 * 32 * kBitSpan key positions per
-// pass, newest first) and advances all of them level by level, so the loads of one level are
-// in flight together instead of one dependent load chain per word.
-#ifndef ROSA_BIT_SPAN
-#define ROSA_BIT_SPAN 1
-#endif
-constexpr int kBitSpan = ROSA_BIT_SPAN;
+// Two stages.  The scan reads the level-1 word of 32 x 32 key positions per step (newest first)
+// and appends the non-empty ones to the queue (ballot + prefix count).  Whenever 32 words are
+// queued, or the scan ends, one batch is extended level by level with every lane holding one
+// word, so the level loop runs on full warps instead of on the few words of a step that have
+// a candidate at all.
+constexpr int kBitQueue = 64;
+
+struct BitCandidate {
+  int word;         // word index on the bitmap axis
+  uint32_t bits;    // level-1 candidates inside it
+};
 
 template <typename Sym>
 __device__ __forceinline__ unsigned long long bit_match_row(const Sym* __restrict__ q,
                                                             const uint32_t* __restrict__ e,
                                                             int64_t mask_words, int start, int i,
-                                                            int W, int lane) {
+                                                            int W, int lane,
+                                                            BitCandidate* __restrict__ queue) {
   const int g_lo = start, g_hi = start + i - 1;
   const int w_lo = g_lo >> 5, w_hi = g_hi >> 5;
   const int q_first = lane <= i ? (int)q[i - lane] : 0;   // lane l: query symbol l rows back
@@ -45,65 +51,79 @@ __device__ __forceinline__ unsigned long long bit_match_row(const Sym* __restric
   // condition
   const int sym_first = __shfl_sync(0xffffffffu, q_first, 0);
   const uint32_t* __restrict__ first_row = e + (int64_t)sym_first * mask_words;
+  const unsigned lanes_below = (1u << lane) - 1u;
   int best_len = 0, best_route = 0;
+  int queued = 0;                                         // same value in every lane
+  bool done = false;                                      // a match reached the horizon
 
-  for (int wtop = w_hi; wtop >= w_lo; wtop -= 32 * kBitSpan) {   // newest positions first
-    uint32_t cur[kBitSpan];
-    int length[kBitSpan];
-    unsigned alive = 0u;                                  // bit c: word c can still extend
-#pragma unroll
-    for (int c = 0; c < kBitSpan; ++c) {
-      const int w = wtop - 32 * c - lane;
-      uint32_t bits = w >= w_lo ? first_row[w] : 0u;
-      if (w == w_hi) bits &= 0xffffffffu >> (31 - (g_hi & 31));
-      if (w == w_lo) bits &= 0xffffffffu << (g_lo & 31);
-      cur[c] = bits;
-      length[c] = bits ? 1 : 0;
-      alive |= bits ? 1u << c : 0u;
-    }
+  // Extends the first min(queued, 32) queue entries to their full match length, keeps the best,
+  // and moves the rest of the queue to the front.
+  auto extend_batch = [&]() {
+    __syncwarp();
+    const bool mine = lane < queued;
+    const int w = mine ? queue[lane].word : 0;
+    uint32_t cur = mine ? queue[lane].bits : 0u;
+    const int spill_w = lane + 32 < queued ? queue[lane + 32].word : 0;
+    const uint32_t spill_bits = lane + 32 < queued ? queue[lane + 32].bits : 0u;
+    int length = mine ? 1 : 0;
+    bool alive = mine;
     int qv = q_first;
-    for (int lev = 1; lev < W && __any_sync(0xffffffffu, alive != 0u); ++lev) {
+    for (int lev = 1; lev < W && __any_sync(0xffffffffu, alive); ++lev) {
       if ((lev & 31) == 0) qv = lev + lane <= i ? (int)q[i - lev - lane] : 0;
       const int sym = __shfl_sync(0xffffffffu, qv, lev & 31);
-      const uint32_t* __restrict__ row = e + (int64_t)sym * mask_words;
-      const int sh = lev & 31;
-#pragma unroll
-      for (int c = 0; c < kBitSpan; ++c) {
-        if (alive >> c & 1u) {
-          // bit g of the shifted bitmap is bit g - lev of E[sym]; it may only extend a match
-          // that still has a predecessor inside the sequence: g - lev >= start
-          const int w = wtop - 32 * c - lane;
-          const int hi_w = w - (lev >> 5);
-          const uint32_t hi = hi_w >= w_lo ? row[hi_w] : 0u;
-          const uint32_t lo = (sh != 0 && hi_w - 1 >= w_lo) ? row[hi_w - 1] : 0u;
-          uint32_t m = __funnelshift_l(lo, hi, sh);
-          const int lim = start + lev - 32 * w;           // bits below lim have no predecessor
-          if (lim > 0) m = lim >= 32 ? 0u : m & (0xffffffffu << lim);
-          const uint32_t next = cur[c] & m;
-          if (next != 0u) {
-            cur[c] = next;
-            length[c] = lev + 1;
-          } else {
-            alive &= ~(1u << c);
-          }
+      if (alive) {
+        // bit g of the shifted bitmap is bit g - lev of E[sym]; it may only extend a match
+        // that still has a predecessor inside the sequence: g - lev >= start
+        const uint32_t* __restrict__ row = e + (int64_t)sym * mask_words;
+        const int sh = lev & 31, hi_w = w - (lev >> 5);
+        const uint32_t hi = hi_w >= w_lo ? row[hi_w] : 0u;
+        const uint32_t lo = (sh != 0 && hi_w - 1 >= w_lo) ? row[hi_w - 1] : 0u;
+        uint32_t m = __funnelshift_l(lo, hi, sh);
+        const int lim = start + lev - 32 * w;             // bits below lim have no predecessor
+        if (lim > 0) m = lim >= 32 ? 0u : m & (0xffffffffu << lim);
+        const uint32_t next = cur & m;
+        if (next != 0u) {
+          cur = next;
+          length = lev + 1;
+        } else {
+          alive = false;
         }
       }
     }
-#pragma unroll
-    for (int c = 0; c < kBitSpan; ++c) {
-      if (length[c] > 0) {
-        const int w = wtop - 32 * c - lane;
-        const int pos = 32 * w + 31 - __clz(cur[c]);      // latest position of the longest match
-        const int route = pos - start + 1;
-        if (length[c] > best_len || (length[c] == best_len && route > best_route)) {
-          best_len = length[c];
-          best_route = route;
-        }
+    if (length > 0) {
+      const int pos = 32 * w + 31 - __clz(cur);           // latest position of the longest match
+      const int route = pos - start + 1;
+      if (length > best_len || (length == best_len && route > best_route)) {
+        best_len = length;
+        best_route = route;
       }
     }
-    // newer positions were examined first: nothing older can beat a match at the horizon
-    if (__reduce_max_sync(0xffffffffu, best_len) >= W) break;
+    __syncwarp();
+    if (lane + 32 < queued) {
+      queue[lane].word = spill_w;
+      queue[lane].bits = spill_bits;
+    }
+    queued = queued > 32 ? queued - 32 : 0;
+    // newer positions are queued first: nothing later in the queue or older on the axis can
+    // beat a match at the horizon
+    done = __any_sync(0xffffffffu, best_len >= W);
+  };
+
+  for (int wb = w_hi; wb >= w_lo && !done; wb -= 32) {    // newest positions first
+    const int w = wb - lane;
+    uint32_t bits = w >= w_lo ? first_row[w] : 0u;
+    if (w == w_hi) bits &= 0xffffffffu >> (31 - (g_hi & 31));
+    if (w == w_lo) bits &= 0xffffffffu << (g_lo & 31);
+    const unsigned hit = __ballot_sync(0xffffffffu, bits != 0u);
+    if (bits != 0u) {
+      const int slot = queued + __popc(hit & lanes_below);
+      queue[slot].word = w;
+      queue[slot].bits = bits;
+    }
+    queued += __popc(hit);
+    if (queued >= 32) extend_batch();
   }
+  while (queued > 0 && !done) extend_batch();
   const int row_len = __reduce_max_sync(0xffffffffu, best_len);
   const int row_route = __reduce_max_sync(0xffffffffu, best_len == row_len ? best_route : 0);
   return row_len > 0 ? ((unsigned long long)(unsigned)row_len << 32) | (unsigned)row_route : 0ull;

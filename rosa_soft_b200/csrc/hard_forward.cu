@@ -285,8 +285,9 @@ __global__ void __launch_bounds__(kBitsWarps * 32)
   const bool dense = plan.cu_seqlens == nullptr;
   const int32_t* __restrict__ q = qsym + (int64_t)seq * sym_seq_stride +
                                   (int64_t)h * sym_head_stride + (dense ? 0 : start);
-  const unsigned long long key =
-      bit_match_row(q, masks + ((int64_t)h << D) * mask_words, mask_words, start, i, W, lane);
+  __shared__ BitCandidate queues[kBitsWarps][kBitQueue];
+  const unsigned long long key = bit_match_row(q, masks + ((int64_t)h << D) * mask_words, mask_words,
+                                               start, i, W, lane, queues[threadIdx.x >> 5]);
   if (lane == 0) *out = key;
 }
 

@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(kStreamWarps * 32)
                         const uint8_t* __restrict__ query_history,
                         unsigned long long* __restrict__ best,
                         const int32_t* __restrict__ status) {
+  __shared__ BitCandidate queues[kStreamWarps][kBitQueue];
   if (status[0] != 0) return;
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kStreamWarps + (threadIdx.x >> 5);
@@ -108,7 +109,7 @@ __global__ void __launch_bounds__(kStreamWarps * 32)
     const int64_t sh = (int64_t)s * H + h;
     key = bit_match_row(query_history + sh * capacity,
                         key_masks + (sh << qk_bits) * (capacity >> 5), capacity >> 5, 0, i, W,
-                        lane);
+                        lane, queues[threadIdx.x >> 5]);
   }
   if (lane == 0) best[token * H + h] = key;
 }
