@@ -30,8 +30,11 @@ namespace rosa {
 // and appends the non-empty ones to the queue (ballot + prefix count).  Whenever 32 words are
 // queued, or the scan ends, one batch is extended level by level with every lane holding one
 // word, so the level loop runs on full warps instead of on the few words of a step that have
-// a candidate at all.
+// a candidate at all.  Random candidates die within a level or two; when only a couple of
+// words are left they are finished with the lanes spread over 32 levels at once, so a match
+// of length L costs about L / 32 steps instead of L.
 constexpr int kBitQueue = 64;
+constexpr int kBitFewWords = 2;   // at most this many live words: switch to level-parallel
 
 struct BitCandidate {
   int word;         // word index on the bitmap axis
@@ -46,10 +49,9 @@ __device__ __forceinline__ unsigned long long bit_match_row(const Sym* __restric
                                                             BitCandidate* __restrict__ queue) {
   const int g_lo = start, g_hi = start + i - 1;
   const int w_lo = g_lo >> 5, w_hi = g_hi >> 5;
-  const int q_first = lane <= i ? (int)q[i - lane] : 0;   // lane l: query symbol l rows back
   // every warp-wide primitive below is executed by all 32 lanes, never under a per-lane
   // condition
-  const int sym_first = __shfl_sync(0xffffffffu, q_first, 0);
+  const int sym_first = (int)q[i];
   const uint32_t* __restrict__ first_row = e + (int64_t)sym_first * mask_words;
   const unsigned lanes_below = (1u << lane) - 1u;
   int best_len = 0, best_route = 0;
@@ -67,21 +69,57 @@ __device__ __forceinline__ unsigned long long bit_match_row(const Sym* __restric
     const uint32_t spill_bits = lane + 32 < queued ? queue[lane + 32].bits : 0u;
     int length = mine ? 1 : 0;
     bool alive = mine;
-    int qv = q_first;
-    for (int lev = 1; lev < W && __any_sync(0xffffffffu, alive); ++lev) {
-      if ((lev & 31) == 0) qv = lev + lane <= i ? (int)q[i - lev - lane] : 0;
-      const int sym = __shfl_sync(0xffffffffu, qv, lev & 31);
+    // Shifted bitmap word of one level: bit g of it is bit g - lev of E[q_{i-lev}]; a bit may
+    // only extend a match that still has a predecessor inside the sequence (g - lev >= start).
+    auto level_mask = [&](int lev, int word) -> uint32_t {
+      const uint32_t* __restrict__ row = e + (int64_t)q[i - lev] * mask_words;
+      const int sh = lev & 31, hi_w = word - (lev >> 5);
+      const uint32_t hi = hi_w >= w_lo ? row[hi_w] : 0u;
+      const uint32_t lo = (sh != 0 && hi_w - 1 >= w_lo) ? row[hi_w - 1] : 0u;
+      uint32_t m = __funnelshift_l(lo, hi, sh);
+      const int lim = start + lev - 32 * word;            // bits below lim have no predecessor
+      if (lim > 0) m = lim >= 32 ? 0u : m & (0xffffffffu << lim);
+      return m;
+    };
+    // `lev` symbols are matched by every word still alive (its length equals lev).
+    for (int lev = 1; lev < W && lev <= i; ++lev) {
+      const unsigned alive_lanes = __ballot_sync(0xffffffffu, alive);
+      if (alive_lanes == 0u) break;
+      if (__popc(alive_lanes) <= kBitFewWords) {
+        // Few words left, possibly with long matches: finish them one by one with the LANES
+        // spread over 32 consecutive levels.  An inclusive AND scan of the level masks gives the
+        // survivors after each level; the matches end at the first level with none.
+        for (unsigned rest = alive_lanes; rest != 0u; rest &= rest - 1u) {
+          const int src = __ffs(rest) - 1;
+          const int word = __shfl_sync(0xffffffffu, w, src);
+          uint32_t word_bits = __shfl_sync(0xffffffffu, cur, src);
+          int word_len = lev;
+          for (int base = lev; base < W && base <= i; base += 32) {
+            const int level = base + lane;
+            uint32_t m = (level < W && level <= i) ? level_mask(level, word) : 0u;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+              const uint32_t up = __shfl_up_sync(0xffffffffu, m, d);
+              if (lane >= d) m &= up;
+            }
+            const uint32_t left = word_bits & m;           // survivors after level base + lane
+            const unsigned ok = __ballot_sync(0xffffffffu, left != 0u);   // a prefix of ones
+            const int passed = ok == 0xffffffffu ? 32 : __ffs(~ok) - 1;
+            if (passed > 0) {
+              word_bits = __shfl_sync(0xffffffffu, left, passed - 1);
+              word_len = base + passed;
+            }
+            if (passed < 32) break;
+          }
+          if (lane == src) {
+            cur = word_bits;
+            length = word_len;
+          }
+        }
+        break;
+      }
       if (alive) {
-        // bit g of the shifted bitmap is bit g - lev of E[sym]; it may only extend a match
-        // that still has a predecessor inside the sequence: g - lev >= start
-        const uint32_t* __restrict__ row = e + (int64_t)sym * mask_words;
-        const int sh = lev & 31, hi_w = w - (lev >> 5);
-        const uint32_t hi = hi_w >= w_lo ? row[hi_w] : 0u;
-        const uint32_t lo = (sh != 0 && hi_w - 1 >= w_lo) ? row[hi_w - 1] : 0u;
-        uint32_t m = __funnelshift_l(lo, hi, sh);
-        const int lim = start + lev - 32 * w;             // bits below lim have no predecessor
-        if (lim > 0) m = lim >= 32 ? 0u : m & (0xffffffffu << lim);
-        const uint32_t next = cur & m;
+        const uint32_t next = cur & level_mask(lev, w);
         if (next != 0u) {
           cur = next;
           length = lev + 1;
