@@ -20,7 +20,8 @@
 //             C is the adjoint of log x_n: dQz[i] += m/(2D) C k_z[j], dKz[j] += m/(2D) C q_z[i]
 //   values    dVz[a] += p d gO(i)
 // Sbar and Y are kept in float64 because Y is a difference of long running sums when
-// exact matches are longer than the horizon.
+// exact matches are longer than the horizon (the tensor-core kernel runs Sbar in float32
+// inside a row block while no window product is alive: the recurrence is a contraction then).
 //
 // Schedule: sweep 1 walks every band top-down (rows ascending), produces per-row
 // online-softmax partials and a checkpoint (S, mismatch-window sum) every kVjpRows rows;
