@@ -50,6 +50,9 @@ WORKLOADS = {
     # tokens per slot to a runtime whose state stays on the GPU (the reference's RosaRuntime use)
     "stream": dict(kind="stream", B=64, T=16384, H=64, D=8, Hv=64, Dv=8, W=32, chunk=2048, scale=1.0,
                    p=0.0, m=3.0, dtype="uint8", gen="symbols"),
+    # 8 of the stream workload's slots: small enough for a multi-pass profiler capture
+    "stream_profile": dict(kind="stream", B=8, T=16384, H=64, D=8, Hv=64, Dv=8, W=32, chunk=2048,
+                           scale=1.0, p=0.0, m=3.0, dtype="uint8", gen="symbols"),
     "small": dict(B=1, T=1024, H=8, D=8, Hv=2, Dv=8, W=128, scale=1.0, p=0.1, m=3.0,
                   dtype="bfloat16", gen="randn"),
 }
@@ -213,7 +216,7 @@ def cpu_stream_run(cfg, steps, warmup):
     import numpy as np
     import torch
 
-    sample = dict(cfg, B=16)
+    sample = dict(cfg, B=min(cfg["B"], 16))
     q, k, pay = make_stream_inputs(sample, 7, "cpu")
     B, T, H, chunk = sample["B"], sample["T"], sample["H"], sample["chunk"]
     lib = os.path.join(ROOT, "oracle", "_ref", "librosa_runtime_ref.so")
