@@ -464,3 +464,24 @@ def test_route_inspection_matches_oracle_dense_and_packed():
                                      max_suffix_length=W)
     assert np.array_equal(info.selected_route_indices.t().cpu().numpy(), want_route)
     assert np.array_equal(info.selected_match_lengths.t().cpu().numpy(), want_len)
+
+
+def test_hard_inference_with_a_horizon_beyond_the_narrow_key_range(cabi):
+    """Horizons of 2048 and more take the generic matcher (64-bit candidate keys); a copied
+    stretch of 2600 symbols makes the match length actually pass 2047."""
+    from oracle import rosa_oracle as orc
+    rng = np.random.default_rng(17)
+    T, H, Hp, Dp, W = 6000, 2, 1, 4, 2500
+    k = rng.integers(0, 1 << 32, size=(T, H), dtype=np.uint64).astype(np.uint32)
+    q = rng.integers(0, 1 << 32, size=(T, H), dtype=np.uint64).astype(np.uint32)
+    q[3200:5800] = k[100:2700]            # rows 3200.. match keys 100.. for 2600 steps
+    q[700:760, 1] = k[650:710, 1]
+    pay = rng.standard_normal((T, Hp, Dp)).astype(np.float32)
+    cu_np = np.array([0, T], dtype=np.int64)
+    ref_out, ref_end = orc.hard_inference(q, k, pay, cu_np, W)
+    out, end, _ = cabi.hard_inference(torch.from_numpy(q.view(np.int32)).to(DEV),
+                                      torch.from_numpy(k.view(np.int32)).to(DEV),
+                                      torch.from_numpy(pay).to(DEV), (1, T), W)
+    assert np.array_equal(end.cpu().numpy(), ref_end)
+    assert np.array_equal(out.cpu().numpy(), ref_out)
+    assert int((ref_end[5799] >= 0).sum()) == H      # the long copy really is matched
