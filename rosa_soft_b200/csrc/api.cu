@@ -44,8 +44,10 @@ FwdLayout fwd_layout(int64_t N, int H, int64_t S, bool transposed_symbols) {
     off = align_up(off + (size_t)N * H * sizeof(int32_t));
     l.kt_off = off;
     off = align_up(off + (size_t)N * H * sizeof(int32_t));
-    l.masks_off = 0;
-    l.mask_words = 0;
+    // bitmaps over the symbols hashed to 8 bits (prefilter of the wide-symbol matcher)
+    l.mask_words = (N + 31) / 32 + 1;
+    l.masks_off = off;
+    off = align_up(off + ((size_t)H << kMaskSymbolBits) * (size_t)l.mask_words * sizeof(uint32_t));
   } else {
     // occurrence bitmaps of the bit-parallel matcher, sized for the widest symbol it serves
     // (the sizing function does not know D): H * 2^8 rows of ceil(N / 32) + 1 words
@@ -249,6 +251,8 @@ ROSA_B200_API int rosa_b200_hard_inference(const uint32_t* query_symbols, const 
   a.best = reinterpret_cast<unsigned long long*>(ws + l.best_off);
   a.sym_seq_stride = dense ? uniform_len : 0;  // [H, N] with sequence s starting at s * T
   a.sym_head_stride = N;
+  a.hash_masks = reinterpret_cast<uint32_t*>(ws + l.masks_off);
+  a.mask_words = l.mask_words;
 
   launch_build_plan(a.plan, st);
   ROSA_CUDA_OK(cudaGetLastError());

@@ -277,6 +277,9 @@ struct FwdArgs {
   // the run-length matcher.
   uint32_t* match_masks;
   int64_t mask_words;
+  // Bitmaps over symbols hashed to 8 bits, [H][256][mask_words]: prefilter of the matcher for
+  // wide symbols (batched inference); null when not provided.
+  uint32_t* hash_masks;
 };
 
 int launch_pack_symbols(const void* q, const void* k, int dtype, int64_t N, int H, int D,

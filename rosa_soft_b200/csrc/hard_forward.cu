@@ -89,7 +89,8 @@ __global__ void __launch_bounds__(kFwdWarps * 32)
     hard_match_kernel(Plan plan, const int32_t* __restrict__ qsym,
                       const int32_t* __restrict__ ksym, int64_t sym_seq_stride,
                       int64_t sym_head_stride, int H, int W,
-                      unsigned long long* __restrict__ best) {
+                      unsigned long long* __restrict__ best, const int32_t* __restrict__ run_flag) {
+  if (run_flag != nullptr && *run_flag == 0) return;   // only needed when the prefilter gave up
   int seq, local;
   if (!find_item(plan, blockIdx.x, &seq, &local)) return;
   const int h = blockIdx.y;
@@ -177,7 +178,9 @@ __global__ void __launch_bounds__(kMatchThreads)
     hard_match_fast_kernel(Plan plan, const int32_t* __restrict__ qsym,
                            const int32_t* __restrict__ ksym, int64_t sym_seq_stride,
                            int64_t sym_head_stride, int H, int W,
-                           unsigned long long* __restrict__ best) {
+                           unsigned long long* __restrict__ best,
+                           const int32_t* __restrict__ run_flag) {
+  if (run_flag != nullptr && *run_flag == 0) return;   // only needed when the prefilter gave up
   __shared__ int s_k[kMatchWin];
   __shared__ int s_q[kMatchRows];
   __shared__ unsigned s_best[kMatchRows];
@@ -289,6 +292,108 @@ __global__ void __launch_bounds__(kBitsWarps * 32)
   const unsigned long long key = bit_match_row(q, masks + ((int64_t)h << D) * mask_words, mask_words,
                                                start, i, W, lane, queues[threadIdx.x >> 5]);
   if (lane == 0) *out = key;
+}
+
+// --------------------------------------- hashed prefilter for wide symbols (D > 8)
+// Symbols of up to 32 bits are hashed to 8 bits and the key stream is indexed by the same
+// occurrence bitmaps as above.  The level-1 word of a row then holds every true candidate plus
+// about 1/256 of the other positions; each set bit is verified against the real symbols and
+// extended backwards exactly.  Rows with more than kHashTrueLimit genuine candidates (periodic or
+// constant streams) would cost O(candidates x horizon): they raise a flag instead, and the
+// run-length matcher, whose cost does not depend on the data, then redoes the launch (its
+// atomicMax merges the same exact winners, so rows already resolved keep their value).
+constexpr int kHashTrueLimit = 48;
+
+__device__ __forceinline__ unsigned hash8(unsigned sym) { return (sym * 0x9E3779B1u) >> 24; }
+
+__global__ void build_hash_masks_kernel(Plan plan, const int32_t* __restrict__ ksym, int64_t N,
+                                        int H, int64_t sym_seq_stride, int64_t sym_head_stride,
+                                        uint32_t* __restrict__ masks, int64_t mask_words) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t words = (N + 31) >> 5;
+  if (warp_id >= words * H) return;
+  const int h = (int)(warp_id / words);
+  const int64_t word = warp_id - (int64_t)h * words;
+  const int64_t g = word * 32 + lane;
+  unsigned sym = 0x80000000u | (unsigned)lane;   // lanes past the end match nobody
+  if (g < N) {
+    int start = 0, len = 0;
+    const int seq = find_segment(plan, g, &start, &len);
+    if (seq >= 0) {
+      const bool dense = plan.cu_seqlens == nullptr;
+      sym = hash8((unsigned)ksym[(int64_t)seq * sym_seq_stride + (int64_t)h * sym_head_stride +
+                                 (dense ? g - start : g)]);
+    }
+  }
+  const unsigned peers = __match_any_sync(0xffffffffu, sym);
+  if (sym < 256u && lane == __ffs(peers) - 1)
+    masks[(((int64_t)h << 8) + sym) * mask_words + word] = peers;
+}
+
+__global__ void __launch_bounds__(kBitsWarps * 32)
+    hard_match_hashed_kernel(Plan plan, const int32_t* __restrict__ qsym,
+                             const int32_t* __restrict__ ksym, const uint32_t* __restrict__ masks,
+                             int64_t N, int H, int W, int64_t mask_words, int64_t sym_seq_stride,
+                             int64_t sym_head_stride, unsigned long long* __restrict__ best,
+                             int32_t* __restrict__ overflow_flag) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kBitsWarps + (threadIdx.x >> 5);
+  if (row >= N * H) return;
+  const int h = (int)(row / N);
+  const int64_t g_row = row - (int64_t)h * N;
+  unsigned long long* out = best + g_row * H + h;
+  int start = 0, len = 0;
+  const int seq = find_segment(plan, g_row, &start, &len);
+  const int i = (int)(g_row - start);
+  if (seq < 0 || i == 0) {
+    if (lane == 0) *out = 0ull;
+    return;
+  }
+  const bool dense = plan.cu_seqlens == nullptr;
+  const int64_t base = (int64_t)seq * sym_seq_stride + (int64_t)h * sym_head_stride +
+                       (dense ? 0 : start);
+  const int32_t* __restrict__ q = qsym + base;       // q[p], k[p]: position p of this sequence
+  const int32_t* __restrict__ k = ksym + base;
+  const int q_i = q[i];
+  const uint32_t* __restrict__ e = masks + (((int64_t)h << 8) + hash8((unsigned)q_i)) * mask_words;
+  const int g_lo = start, g_hi = start + i - 1;
+  const int w_lo = g_lo >> 5, w_hi = g_hi >> 5;
+  int best_len = 0, best_route = 0, genuine = 0;
+  bool stop = false;                                  // uniform: set from votes only
+  for (int wb = w_hi; wb >= w_lo && !stop; wb -= 32) {    // newest positions first
+    const int w = wb - lane;
+    uint32_t bits = w >= w_lo ? e[w] : 0u;
+    if (w == w_hi) bits &= 0xffffffffu >> (31 - (g_hi & 31));
+    if (w == w_lo) bits &= 0xffffffffu << (g_lo & 31);
+    // every lane walks the set bits of its own word, newest first (no warp primitive inside)
+    while (bits != 0u) {
+      const int bit = 31 - __clz(bits);
+      bits &= ~(1u << bit);
+      const int j = 32 * w + bit - start;             // key position inside the sequence
+      if (k[j] != q_i) continue;                      // hash collision
+      if (++genuine > kHashTrueLimit) break;          // bounded work per lane and row
+      int length = 1;
+      const int cap = min(W, j + 1);                  // a match cannot start before the sequence
+      while (length < cap && k[j - length] == q[i - length]) ++length;
+      if (length > best_len || (length == best_len && j + 1 > best_route)) {
+        best_len = length;
+        best_route = j + 1;
+      }
+    }
+    const bool over = __any_sync(0xffffffffu, genuine > kHashTrueLimit);
+    // newer positions were examined first: nothing older can beat a match at the horizon
+    stop = over || __reduce_max_sync(0xffffffffu, best_len) >= W;
+    if (over) best_len = 0;
+  }
+  const bool over = __any_sync(0xffffffffu, genuine > kHashTrueLimit);
+  const int row_len = over ? 0 : __reduce_max_sync(0xffffffffu, best_len);
+  const int row_route =
+      over ? 0 : __reduce_max_sync(0xffffffffu, best_len == row_len ? best_route : 0);
+  if (lane == 0) {
+    *out = row_len > 0 ? ((unsigned long long)(unsigned)row_len << 32) | (unsigned)row_route : 0ull;
+    if (over) atomicExch(overflow_flag, 1);
+  }
 }
 
 // ------------------------------------------------------------------- gather
@@ -427,19 +532,47 @@ int launch_hard_match(const FwdArgs& a, int items_upper, cudaStream_t stream) {
     return 0;
   }
   if (items_upper <= 0) return 0;
+  const int32_t* run_flag = nullptr;
+  if (a.hash_masks != nullptr && a.N > 0) {
+    // wide symbols: hashed prefilter first; the run-length matcher below then only runs when
+    // some row had too many genuine candidates (flag in the plan's status words)
+    int32_t* flag = a.plan.status + 2;
+    {
+      ProfileScope prof("build_match_masks", stream);
+      ROSA_CUDA_OK(cudaMemsetAsync(a.hash_masks, 0,
+                                   ((size_t)a.H << 8) * (size_t)a.mask_words * sizeof(uint32_t),
+                                   stream));
+      const int64_t warps = ((a.N + 31) >> 5) * a.H;
+      build_hash_masks_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(
+          a.plan, a.packed_k, a.N, a.H, a.sym_seq_stride, a.sym_head_stride, a.hash_masks,
+          a.mask_words);
+      ROSA_CUDA_OK(cudaGetLastError());
+    }
+    {
+      ProfileScope prof("hard_match_hashed", stream);
+      const int64_t rows = a.N * a.H;
+      hard_match_hashed_kernel<<<(unsigned)((rows + kBitsWarps - 1) / kBitsWarps), kBitsWarps * 32,
+                                 0, stream>>>(a.plan, a.packed_q, a.packed_k, a.hash_masks, a.N, a.H,
+                                              a.W, a.mask_words, a.sym_seq_stride,
+                                              a.sym_head_stride, a.best, flag);
+      ROSA_CUDA_OK(cudaGetLastError());
+    }
+    run_flag = flag;
+  }
   ProfileScope prof("hard_match", stream);
   const int64_t max_len = a.plan.cu_seqlens == nullptr ? a.plan.uniform_len : a.N;
   if (a.W < 2048 && max_len < (1 << 21)) {
     // 32-bit candidate keys: run length in the top 11 bits, route in the low 21
     hard_match_fast_kernel<<<(unsigned)((int64_t)items_upper * a.H), kMatchThreads, 0, stream>>>(
-        a.plan, a.packed_q, a.packed_k, a.sym_seq_stride, a.sym_head_stride, a.H, a.W, a.best);
+        a.plan, a.packed_q, a.packed_k, a.sym_seq_stride, a.sym_head_stride, a.H, a.W, a.best,
+        run_flag);
     ROSA_CUDA_OK(cudaGetLastError());
     return 0;
   }
   dim3 grid((unsigned)items_upper, (unsigned)a.H);
   hard_match_kernel<<<grid, kFwdWarps * 32, 0, stream>>>(a.plan, a.packed_q, a.packed_k,
                                                         a.sym_seq_stride, a.sym_head_stride, a.H,
-                                                        a.W, a.best);
+                                                        a.W, a.best, run_flag);
   ROSA_CUDA_OK(cudaGetLastError());
   return 0;
 }
