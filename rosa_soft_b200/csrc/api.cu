@@ -188,10 +188,13 @@ ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, con
   a.best = reinterpret_cast<unsigned long long*>(ws + l.best_off);
   a.sym_seq_stride = dense ? (int64_t)H * uniform_len : 0;
   a.sym_head_stride = dense ? uniform_len : N;
-  if (D <= kMaskSymbolBits) {
+  // symbols of up to 8 bits index the bitmaps directly; wider ones go through the hashed
+  // prefilter (same 2^8 rows per head)
+  if (D <= kMaskSymbolBits)
     a.match_masks = reinterpret_cast<uint32_t*>(ws + l.masks_off);
-    a.mask_words = l.mask_words;
-  }
+  else
+    a.hash_masks = reinterpret_cast<uint32_t*>(ws + l.masks_off);
+  a.mask_words = l.mask_words;
 
   launch_build_plan(a.plan, st);
   ROSA_CUDA_OK(cudaGetLastError());
