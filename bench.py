@@ -496,7 +496,7 @@ def main():
     per_unit = (80 if kind == "inference" else 12 if kind == "stream" else
                 2 * cfg["D"] * s + cfg["Dv"] * s * cfg["Hv"] / cfg["H"] + cfg["Dv"] * s + 8)
     fwd_bytes = per_unit * cfg["B"] * cfg["T"] * cfg["H"]
-    fwd_ms = sum(kernels.get(n, (0.0, 0))[0] for n in ("pack_symbols", "transpose_symbols", "build_match_masks", "hard_match",
+    fwd_ms = sum(kernels.get(n, (0.0, 0))[0] for n in ("pack_symbols", "transpose_symbols", "build_match_masks", "hard_match", "hard_match_hashed",
                                                        "gather_output", "inference_finish",
                                                        "stream_prepare", "stream_append", "stream_match",
                                                        "stream_finish"))
@@ -532,7 +532,7 @@ def main():
                              "not by the tensor pipe"},
         "roofline_forward": {"bound": "hbm",
                              "kernels": ("stream_append+stream_match+stream_finish" if kind == "stream"
-                                         else "pack_symbols+build_match_masks+hard_match+gather_output"),
+                                         else "pack_symbols+build_match_masks+hard_match(+hashed)+gather_output"),
                              "achieved": fwd_gbs, "peak": hbm_peak, "unit": "GB/s",
                              "frac": (fwd_gbs / hbm_peak) if fwd_gbs else None},
         "kernel_ms_per_step": {n: ms / args.steps for n, (ms, _) in sorted(kernels.items())},
