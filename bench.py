@@ -50,6 +50,9 @@ WORKLOADS = {
     # tokens per slot to a runtime whose state stays on the GPU (the reference's RosaRuntime use)
     "stream": dict(kind="stream", B=64, T=16384, H=64, D=8, Hv=64, Dv=8, W=32, chunk=2048, scale=1.0,
                    p=0.0, m=3.0, dtype="uint8", gen="symbols"),
+    # 8 of the inference workload's streams: small enough for a multi-pass profiler capture
+    "c5_profile": dict(kind="inference", B=8, T=16384, H=64, D=32, Hv=64, Dv=8, W=32, scale=1.0,
+                       p=0.0, m=3.0, dtype="float32", gen="symbols"),
     # 8 of the stream workload's slots: small enough for a multi-pass profiler capture
     "stream_profile": dict(kind="stream", B=8, T=16384, H=64, D=8, Hv=64, Dv=8, W=32, chunk=2048,
                            scale=1.0, p=0.0, m=3.0, dtype="uint8", gen="symbols"),
