@@ -991,6 +991,49 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
       const int dim = k_half ? D : Dv;
       float* part = k_half ? a.dk_part + it.rowslot * D : a.dv_part + (it.rowslot + 1) * Dv;
       const bool vec4 = (dim & 3) == 0;
+      if (vec4 && dim <= 8) {
+        // Rows of at most 8 components (the common shapes): the partial rows of all chunks are
+        // read first, so their latencies overlap instead of chaining load -> add -> store three
+        // times.
+        float4 prior[3][2];
+        float* dst3[3];
+        bool use3[3];
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) {
+          const int c = tcl::chunk_start(ch) + 32 * quarter + lane;
+          const int j = b.jwin + c;
+          use3[ch] = (ch < 2 || (quarter == 3 && c >= 256)) && c < ncols && j >= 0 &&
+                     j <= it.len - 1 - b.dmin;
+          const int i_top = min(j + b.dmax, it.len - 1);
+          const bool first = (b.w == it.w_begin) && (b.rb == i_top / kVjpRows);
+          dst3[ch] = part + (int64_t)j * dim;
+#pragma unroll
+          for (int d4 = 0; d4 < 2; ++d4) {
+            prior[ch][d4] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (use3[ch] && !first && 4 * d4 < dim)
+              prior[ch][d4] = reinterpret_cast<const float4*>(dst3[ch])[d4];
+          }
+        }
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) {
+          if (ch == 2 && quarter < 3) continue;
+          float v[16];
+          tc::tmem_ld16(tmem + lane_base + (k_half ? kColK + ch * NK : kColV + ch * NV), v);
+          if (use3[ch]) {
+#pragma unroll
+            for (int d4 = 0; d4 < 2; ++d4) {
+              if (4 * d4 < dim) {
+                float4 o = prior[ch][d4];
+                o.x += v[4 * d4 + 0];
+                o.y += v[4 * d4 + 1];
+                o.z += v[4 * d4 + 2];
+                o.w += v[4 * d4 + 3];
+                reinterpret_cast<float4*>(dst3[ch])[d4] = o;
+              }
+            }
+          }
+        }
+      } else
 #pragma unroll
       for (int ch = 0; ch < 3; ++ch) {
         // only window columns >= 256 of the last chunk are new: they sit in the last quarter
