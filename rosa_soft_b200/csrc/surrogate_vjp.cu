@@ -1210,14 +1210,10 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
         const int r = tid - 48;
         pf0 = r < gn.nrows ? (uint32_t)__ldg(q + gn.i0 + r) : 0u;
       } else if (tid < 128) {
-        // component e & 3 of row e >> 2; the maximum (component 0) becomes the exponent bias,
-        // which needs log i (component 3) from three lanes up
+        // component e & 3 of row e >> 2 (turned into the exponent bias when it is stored)
         const int e = tid - 64;
-        float comp = 0.0f;
-        if ((e >> 2) < gn.nrows) comp = reinterpret_cast<const float*>(rowstat + gn.i0)[e];
-        const float log_i = __shfl_down_sync(0xffffffffu, comp, 3);
-        if ((e & 3) == 0) comp = exponent_bias(comp, log_i);
-        pf0 = __float_as_uint(comp);
+        if ((e >> 2) < gn.nrows)
+          pf0 = __float_as_uint(reinterpret_cast<const float*>(rowstat + gn.i0)[e]);
       } else if (kDropout) {
         const int e = tid - 128;
         if (e < gn.nrows * kVjpWarps) pf0 = a.keepbits[(gn.ck_idx * kVjpRows) * kVjpWarps + e];
@@ -1304,7 +1300,12 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
       } else if (tid < 64) {
         nx.s_q[tid - 48] = (int)pf0;
       } else if (tid < 128) {
-        reinterpret_cast<uint32_t*>(nx.rstat)[tid - 64] = pf0;
+        // the maximum (component 0) becomes the exponent bias, which needs log i (component 3)
+        // from three lanes up; done here, where the loaded words have arrived
+        float comp = __uint_as_float(pf0);
+        const float log_i = __shfl_down_sync(0xffffffffu, comp, 3);
+        if (((tid - 64) & 3) == 0) comp = exponent_bias(comp, log_i);
+        reinterpret_cast<float*>(nx.rstat)[tid - 64] = comp;
       } else if (kDropout) {
         nx.s_keep[tid - 128] = pf0;
       }
