@@ -1125,6 +1125,21 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
                ? load_as_float(a.go, (((int64_t)it.start + g.i0 + r) * a.H + it.h) * Dv + d, a.dtype)
                : 0.0f;
   };
+  // The same element as raw bits (zero for padding): the prefetch keeps loads free of dependent
+  // instructions, so a warp does not sit on the load latency while it still has work to issue;
+  // the conversion happens where the value is stored.
+  auto go_bits = [&](const Geom& g, int e) -> uint32_t {
+    const int r = e / NV, d = e - r * NV;
+    if (!(d < Dv && r < g.nrows)) return 0u;
+    const int64_t idx = (((int64_t)it.start + g.i0 + r) * a.H + it.h) * Dv + d;
+    return a.dtype == ROSA_B200_F32 ? static_cast<const uint32_t*>(a.go)[idx]
+                                    : (uint32_t) static_cast<const uint16_t*>(a.go)[idx];
+  };
+  auto go_from_bits = [&](uint32_t bits) {
+    if (a.dtype == ROSA_B200_F32) return __uint_as_float(bits);
+    if (a.dtype == ROSA_B200_F16) return __half2float(__ushort_as_half((unsigned short)bits));
+    return __uint_as_float(bits << 16);          // bf16 is the upper half of a float
+  };
   // straight global -> shared fill of one table set (first block of a band)
   auto fill_direct = [&](const Geom& g, const SweepSmem& t) {
     fill_block_windows<true>(t, it, q, k, vb, g.i0, g.nrows, g.jwin, kWinCols, kWindowed, W, false);
@@ -1191,7 +1206,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     //        48-63  query symbol          64-127 row statistics (16 x float4)    128-255 keep ballots
     uint32_t pf0 = 0u, pf1 = 0u;
     constexpr int kGoRegs = (kVjpRows * NV + kVjpBand - 1) / kVjpBand;
-    float pgo[kGoRegs];
+    uint32_t pgo[kGoRegs];
     int2 pck = make_int2(0, 0);
     if (next_same) {
       const Geom gn = geom_of(w, rb - 1);
@@ -1221,7 +1236,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
 #pragma unroll
       for (int x = 0; x < kGoRegs; ++x) {
         const int e = tid + x * kVjpBand;
-        pgo[x] = e < kVjpRows * NV ? go_value(gn, e) : 0.0f;
+        pgo[x] = e < kVjpRows * NV ? go_bits(gn, e) : 0u;
       }
       pck = a.ckpt[gn.ck_idx * kVjpBand + tid];
     }
@@ -1312,7 +1327,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
 #pragma unroll
       for (int x = 0; x < kGoRegs; ++x) {
         const int e = tid + x * kVjpBand;
-        if (e < kVjpRows * NV) nx.rest[e] = pgo[x];
+        if (e < kVjpRows * NV) nx.rest[e] = go_from_bits(pgo[x]);
       }
       reinterpret_cast<int2*>(nx.rest + kVjpRows * NV)[tid] = pck;
     } else if (has_next) {
