@@ -1528,12 +1528,16 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
 __global__ void vjp_finalize_kernel(VjpArgs a, int which) {
   const int dim = which == 2 ? a.Dv : a.D;
   const int heads = which == 2 ? a.Hv : a.H;
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= a.N * heads * dim) return;
-  const int d = (int)(idx % dim);
-  const int64_t th = idx / dim;
-  const int64_t token = th / heads;
-  const int hh = (int)(th - token * heads);
+  // Threads run head-major over (head, token, component): the partial rows of one head and item
+  // are contiguous over (token, component), so the reads of a warp coalesce; only the final
+  // element access is strided by the head count.
+  const int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (lin >= a.N * heads * dim) return;
+  const int hh = (int)(lin / (a.N * dim));
+  const int64_t rem = lin - (int64_t)hh * a.N * dim;
+  const int64_t token = rem / dim;
+  const int d = (int)(rem - token * dim);
+  const int64_t idx = (token * heads + hh) * dim + d;
   int start, len;
   const int seq = find_segment(a.plan, token, &start, &len);
   float sum = 0.0f;
