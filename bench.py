@@ -525,10 +525,10 @@ def main():
         "roofline": {"bound": "tensor", "kernel": "vjp_sweep2", "achieved": achieved,
                      "peak": tensor_peak, "unit": "TFLOP/s",
                      "frac": (achieved / tensor_peak) if achieved else None,
-                     # dram__bytes_read + dram__bytes_write of one launch: 0.979 B per causal pair,
+                     # dram__bytes_read + dram__bytes_write of one launch: 0.986 B per causal pair,
                      # captured with ncu on the `profile` workload (268.4 M pairs) and scaled by
                      # pairs -- checkpoints, keep ballots and partials all grow with the pairs
-                     "traffic": (0.979 * pairs) if flop else None,
+                     "traffic": (0.986 * pairs) if flop else None,
                      "peak_source": peak_note,
                      "note": "algorithmic contraction work (6D+4Dv FLOP per causal pair) over the "
                              "kernel's mean launch time; the kernel is bound by CUDA-core issue, "
