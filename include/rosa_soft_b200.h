@@ -51,7 +51,9 @@ enum rosa_b200_status {
   ROSA_B200_STATUS_BAD_FIRST_OFFSET = 1, /* cu_seqlens[0] != 0            */
   ROSA_B200_STATUS_NOT_MONOTONE = 2,     /* cu_seqlens decreases somewhere */
   ROSA_B200_STATUS_BAD_LAST_OFFSET = 3,  /* cu_seqlens[-1] != N            */
-  ROSA_B200_STATUS_CAPACITY = 4          /* a slot would outgrow the history capacity */
+  ROSA_B200_STATUS_CAPACITY = 4,         /* a slot would outgrow the history capacity */
+  ROSA_B200_STATUS_MMA_TIMEOUT = 5       /* a bounded wait on the tensor core gave up: the
+                                            gradients of that call are incomplete */
 };
 
 ROSA_B200_API int rosa_b200_abi_version(void);
@@ -86,7 +88,12 @@ ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, con
  * array's device address (cudaGetSymbolAddress, with that device current); make that first
  * call before starting any stream capture.  All calls on one GPU share the array, which
  * keeps the previous call's contents: the parts that must start at zero are cleared on
- * `stream` by each call, and calls that overlap on the same GPU race -- order them. */
+ * `stream` by each call, and calls that overlap on the same GPU race -- order them.
+ * An inconsistent `cu_seqlens` makes the call a no-op with zero outputs, like the workspace
+ * variant; rosa_b200_read_status(NULL, stream, &status) reports it.  The variant always uses
+ * the run-length matcher (one symbol compare per causal pair): it has no room for the
+ * occurrence bitmaps of the bit-parallel matchers, so on symbols of up to 8 bits it is several
+ * times slower than rosa_b200_hard_forward; results are identical. */
 ROSA_B200_API int rosa_b200_hard_forward_static(
     const void* query, const void* key, const void* value, int dtype, int64_t N, int H, int D,
     int Hv, int Dv, const int32_t* cu_seqlens, int64_t num_seq, int64_t uniform_len,
@@ -190,9 +197,20 @@ ROSA_B200_API void rosa_b200_profile_enable(int on);
 ROSA_B200_API int rosa_b200_profile_collect(const char** names, float* total_ms, int* launches,
                                             int capacity);
 
-/* Copies the status word of the last call that used `workspace` to the host.
- * This is the one entry point that synchronises `stream`. */
+/* Copies the status of the last call that used `workspace` to the host: the offsets check
+ * (1..3), the capacity check of the streaming update (4), or ROSA_B200_STATUS_MMA_TIMEOUT when
+ * a CTA of the backward gave up its bounded wait for the tensor core (it then skips its
+ * remaining accumulator read-backs, so the gradients are incomplete, but the context stays
+ * usable).  `workspace == NULL` reads the status of the last rosa_b200_hard_forward_static
+ * call on the current device (its scratch is inside the library, so the caller has no pointer
+ * to pass).  This is the one entry point that synchronises `stream`. */
 ROSA_B200_API int rosa_b200_read_status(const void* workspace, void* stream, int* status);
+
+/* The decoding rosa_b200_read_status applies to the two device status words (plan word, tensor-core
+ * word), as a pure host function: the plan's code when it is non-zero, else
+ * ROSA_B200_STATUS_MMA_TIMEOUT when the second word is set, else ROSA_B200_STATUS_OK.  No
+ * counterpart in the reference (its kernels assert on the device instead of reporting). */
+ROSA_B200_API int rosa_b200_decode_status(int plan_word, int mma_word);
 
 #ifdef __cplusplus
 }

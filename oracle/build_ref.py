@@ -1,7 +1,7 @@
 """Compile the reference's own RosaRuntime (CPU suffix automaton) into oracle/_ref/.
 
 The single source file is compiled where it lies in the mounted reference tree
-(``$ROSA_REFERENCE_ROOT``, or the default mount point below); nothing is copied into
+(``$ROSA_REFERENCE_ROOT``, or a checkout named ``reference`` beside this repository); nothing is copied into
 this repository and the output directory is git-ignored.  The shared object is
 used by the tests to validate the oracle's restatement of the match semantics
 and by the benchmark as the reference CPU baseline of the hard-inference path.
@@ -20,7 +20,8 @@ OUT_LIB = os.path.join(OUT_DIR, "librosa_runtime_ref.so")
 
 
 def build(reference_root: str | None = None, force: bool = False) -> str | None:
-    root = reference_root or os.environ.get("ROSA_REFERENCE_ROOT", "/root/reference")
+    root = (reference_root or os.environ.get("ROSA_REFERENCE_ROOT")
+            or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
     src = os.path.join(root, "rosa_soft", "csrc", "rosa_runtime.cpp")
     if not os.path.exists(src):
         return OUT_LIB if os.path.exists(OUT_LIB) else None

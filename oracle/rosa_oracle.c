@@ -217,7 +217,13 @@ ORACLE_API void oracle_hard_inference(const uint32_t* qsym, const uint32_t* ksym
 
 /* ---------------------------------------------------------- surrogate VJP */
 
-static inline int popcount32(uint32_t x) { return __builtin_popcount(x); }
+/* bit count without a library call (the build does not assume a popcnt instruction) */
+static inline int popcount32(uint32_t x) {
+  x = x - ((x >> 1) & 0x55555555u);
+  x = (x & 0x33333333u) + ((x >> 2) & 0x33333333u);
+  x = (x + (x >> 4)) & 0x0F0F0F0Fu;
+  return (int)((x * 0x01010101u) >> 24);
+}
 
 /* One (segment, head): accumulates dQz, dKz for this head and dVz for its value
  * head.  All arrays are local to the segment (index 0 = first token).
@@ -242,7 +248,9 @@ static void vjp_one(const uint32_t* qs, const uint32_t* ks, /* [len] symbols of 
   double* prob = (double*)malloc(sizeof(double) * (size_t)len);
   double* dS = (double*)malloc(sizeof(double) * (size_t)len);
   double* pref = (double*)malloc(sizeof(double) * (size_t)(W + 1));
-  double* C = (double*)calloc((size_t)len * (size_t)len, sizeof(double)); /* cell adjoints */
+  /* cell adjoints, stored diagonal-major (cell (p, j) at [(p - j) * len + j]): a route's
+   * window walks one diagonal, so its updates touch consecutive memory */
+  double* C = (double*)calloc((size_t)len * (size_t)len, sizeof(double));
   double* u = (double*)malloc(sizeof(double) * (size_t)len);
   double* dmul = (double*)malloc(sizeof(double) * (size_t)len);
 
@@ -303,9 +311,10 @@ static void vjp_one(const uint32_t* qs, const uint32_t* ks, /* [len] symbols of 
         pref[s] = prod;
       }
       double tail = 0.0;
+      double* diag = C + (i - j) * len + j; /* cell (i - s, j - s) is diag[-s] */
       for (int64_t s = steps - 1; s >= 0; --s) {
         tail += pref[s];
-        C[(i - s) * len + (j - s)] += dS[j] * tail;
+        diag[-s] += dS[j] * tail;
       }
     }
   }
@@ -313,7 +322,7 @@ static void vjp_one(const uint32_t* qs, const uint32_t* ks, /* [len] symbols of 
     const double coef = m / (2.0 * (double)D);
     for (int64_t i = 1; i < len; ++i)
       for (int64_t j = 0; j < i; ++j) {
-        const double cc = coef * C[i * len + j];
+        const double cc = coef * C[(i - j) * len + j];
         if (cc == 0.0) continue;
         for (int d = 0; d < D; ++d) {
           const double kz = ((ks[j] >> d) & 1u) ? 1.0 : -1.0;
@@ -387,8 +396,11 @@ ORACLE_API void oracle_surrogate_vjp(const float* q, const float* k, const float
               dq[idx] = dQz[t * D + d] / (den * den);
             }
             if (dk) {
+              /* the last position of a sequence is never a key (routes end at a - 1 = len - 2):
+               * the reference slices it away before the sign function, so its gradient is an
+               * exact zero whatever the input holds, NaN included */
               const double den = 1.0 + fabs((double)k[idx]);
-              dk[idx] = dKz[t * D + d] / (den * den);
+              dk[idx] = (t == len - 1) ? 0.0 : dKz[t * D + d] / (den * den);
             }
           }
       }

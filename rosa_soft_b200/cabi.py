@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "rosa_b200_stream_workspace_bytes",
     "rosa_b200_stream_update",
     "rosa_b200_read_status",
+    "rosa_b200_decode_status",
     "rosa_b200_profile_enable",
     "rosa_b200_profile_collect",
 )
@@ -75,6 +76,8 @@ def load() -> ctypes.CDLL:
                                             vp, vp, vp, i64, i64, vp, vp, vp, sz, vp]
     lib.rosa_b200_read_status.restype = i32
     lib.rosa_b200_read_status.argtypes = [vp, vp, ctypes.POINTER(i32)]
+    lib.rosa_b200_decode_status.restype = i32
+    lib.rosa_b200_decode_status.argtypes = [i32, i32]
     lib.rosa_b200_profile_enable.restype = None
     lib.rosa_b200_profile_enable.argtypes = [i32]
     lib.rosa_b200_profile_collect.restype = i32
@@ -270,9 +273,12 @@ def stream_update(query, key, payload, chunk_offsets, qk_bits, payload_bits, max
 
 
 def read_status(ws, stream=None) -> int:
+    """Status of the last call that used the workspace tensor ``ws``; ``ws=None`` asks for the last
+    workspace-free forward on the current device.  Synchronises the stream."""
     import torch
 
-    st = stream if stream is not None else torch.cuda.current_stream(ws.device).cuda_stream
+    device = ws.device if ws is not None else None
+    st = stream if stream is not None else torch.cuda.current_stream(device).cuda_stream
     status = ctypes.c_int(0)
     check(load().rosa_b200_read_status(_ptr(ws), ctypes.c_void_p(st), ctypes.byref(status)))
     return status.value

@@ -8,6 +8,7 @@
 
 namespace rosa {
 const char* get_error();
+int static_scratch_for_current_device(void** out);
 void profile_enable(bool on);
 int profile_collect(const char** names, float* total_ms, int* launches, int capacity);
 }
@@ -147,6 +148,12 @@ int check_problem(int64_t N, int H, int D, int Hv, int Dv, const int32_t* cu, in
 }
 
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+
+// The plan's problem (bad offsets, capacity) comes first: it explains everything after it.
+inline int decode_status_words(int plan_word, int mma_word) {
+  if (plan_word != ROSA_B200_STATUS_OK) return plan_word;
+  return mma_word != 0 ? ROSA_B200_STATUS_MMA_TIMEOUT : ROSA_B200_STATUS_OK;
+}
 
 }  // namespace
 
@@ -419,13 +426,25 @@ ROSA_B200_API int rosa_b200_profile_collect(const char** names, float* total_ms,
 }
 
 ROSA_B200_API int rosa_b200_read_status(const void* workspace, void* stream, int* status) {
-  ROSA_REQUIRE(workspace && status, "null pointer argument");
-  int32_t host = 0;
-  ROSA_CUDA_OK(cudaMemcpyAsync(&host, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost,
+  ROSA_REQUIRE(status != nullptr, "null pointer argument");
+  if (workspace == nullptr) {
+    // the scratch of the workspace-free forward: its plan (status words first) opens the array
+    void* scratch = nullptr;
+    if (int rc = rosa::static_scratch_for_current_device(&scratch)) return rc;
+    workspace = scratch;
+  }
+  // word 0: offsets / capacity check of the plan; word 1: a tensor-core wait gave up
+  int32_t host[2] = {0, 0};
+  ROSA_CUDA_OK(cudaMemcpyAsync(host, workspace, sizeof(host), cudaMemcpyDeviceToHost,
                                as_stream(stream)));
   ROSA_CUDA_OK(cudaStreamSynchronize(as_stream(stream)));
-  *status = host;
+  *status = decode_status_words(host[0], host[1]);
   return 0;
+}
+
+// Host-side decoding of the two status words, exported for tests of the decoding itself.
+ROSA_B200_API int rosa_b200_decode_status(int plan_word, int mma_word) {
+  return decode_status_words(plan_word, mma_word);
 }
 
 }  // extern "C"

@@ -34,7 +34,11 @@ constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
 void* g_scratch_ptr[kMaxDevices] = {};
 
+}  // namespace
+
+namespace rosa {
 // Once per device, with that device current: resolve the device address of the array.
+// (Also used by rosa_b200_read_status to find the status words of the last static call.)
 int static_scratch_for_current_device(void** out) {
   int dev = -1;
   ROSA_CUDA_OK(cudaGetDevice(&dev));
@@ -49,8 +53,7 @@ int static_scratch_for_current_device(void** out) {
   *out = g_scratch_ptr[dev];
   return 0;
 }
-
-}  // namespace
+}  // namespace rosa
 
 extern "C" ROSA_B200_API int rosa_b200_hard_forward_static(
     const void* query, const void* key, const void* value, int dtype, int64_t N, int H, int D,

@@ -979,7 +979,21 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   // Reads the accumulators of a finished block and adds them to the per-item partials.
   auto epilogue = [&](int block_w, int block_rb) {
     const Geom b = geom_of(block_w, block_rb);
-    if (!tc::mbar_wait(mbar, mma_phase, 1u << 24)) mma_timed_out = true;
+    // A wait that gave up ends this warp's use of the tensor core: nothing accumulated may be
+    // trusted, so it issues, waits for and reads back nothing more (its partial rows stay
+    // incomplete and the status word tells the host).  The decision is taken per warp (a vote),
+    // because the accumulator loads below are warp-wide instructions; the named barriers of the
+    // row-sum part are still joined so that no warp waits for one that gave up.
+    if (!mma_timed_out && !__all_sync(0xffffffffu, tc::mbar_wait(mbar, mma_phase, 1u << 24)))
+      mma_timed_out = true;
+    if (mma_timed_out) {
+      if ((mask & 1) && warp >= 4 && warp < 7)
+        for (int n0 = 0; n0 < NK; n0 += 16) {
+          asm volatile("bar.sync 1, 96;" ::: "memory");
+          if (n0 + 16 < NK) asm volatile("bar.sync 1, 96;" ::: "memory");
+        }
+      return;
+    }
     mma_phase ^= 1u;
     tc::fence_after_thread_sync();
     const int quarter = warp & 3;
@@ -1444,7 +1458,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
     // those of p*d, and the row-sum k-loop is sliced over the issuers (one accumulator per
     // slice, added in the epilogue).  Each issuer commits once; the mbarrier expects four
     // arrivals.
-    if (lane == 0 && warp < 4) {
+    if (lane == 0 && warp < 4 && !mma_timed_out) {
       tc::fence_after_thread_sync();
       constexpr uint32_t idK = tc::idesc_bf16_f32(128, NK, true, false);
       constexpr uint32_t idV = tc::idesc_bf16_f32(128, NV, true, false);
@@ -1518,7 +1532,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
   }
   if (prev_pending) epilogue(prev_w, prev_rb);
   __syncthreads();
-  if (mma_timed_out && tid == 0) atomicExch(a.plan.status + 1, 1);
+  if (mma_timed_out && lane == 0) atomicExch(a.plan.status + 1, 1);
   if (warp == 0) tc::tmem_dealloc(tmem, kTmemCols);
 }
 
@@ -1565,7 +1579,9 @@ __global__ void vjp_finalize_kernel(VjpArgs a, int which) {
   const float den = 1.0f + fabsf(xv);
   const float coef = which == 2 ? 1.0f : a.mismatch_scale / (2.0f * (float)a.D);
   float* dst = which == 0 ? a.dq : which == 1 ? a.dk : a.dv;
-  dst[idx] = coef * sum / (den * den);
+  // the last position of a sequence is never a key: exact zero, whatever the input holds
+  const bool never_key = which == 1 && seq >= 0 && token - start == len - 1;
+  dst[idx] = never_key ? 0.0f : coef * sum / (den * den);
 }
 
 template <int DPAD, int DVPAD>

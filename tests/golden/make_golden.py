@@ -1,7 +1,7 @@
 """Generate golden input/output vectors by running the UNMODIFIED reference.
 
-Run in a container where the reference tree is mounted (``$ROSA_REFERENCE_ROOT``, or the
-default mount point below):  ``python tests/golden/make_golden.py``.
+Run in a container where the reference tree is mounted, with ``$ROSA_REFERENCE_ROOT`` naming
+its root:  ``ROSA_REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py``.
 It imports ``rosa_soft`` from that tree (pure-PyTorch ``reference`` variant, CPU)
 and, when ``oracle/_ref/librosa_runtime_ref.so`` has been built by
 ``oracle/build_ref.py``, the reference's own RosaRuntime.  The ``.npz`` files it
@@ -18,7 +18,9 @@ import os
 import sys
 
 sys.dont_write_bytecode = True
-REFERENCE_ROOT = os.environ.get("ROSA_REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("ROSA_REFERENCE_ROOT")
+if not REFERENCE_ROOT or not os.path.isdir(os.path.join(REFERENCE_ROOT, "rosa_soft")):
+    raise SystemExit("set ROSA_REFERENCE_ROOT to the root of the reference checkout")
 sys.path.insert(0, REFERENCE_ROOT)
 
 import numpy as np
@@ -65,6 +67,24 @@ def dense_case(name, B, T, H, D, Hv, Dv, W, scale, p, m, dtype, seed, mode="rand
         reps = (T + 4) // 5
         q = (base.repeat(1, reps, 1, 1)[:, :T] * 0.7).to(dt)
         k = q.clone()
+    elif mode == "repeat":
+        # token stream over alphabet 2^D in which earlier segments are copied: long exact matches
+        rng = np.random.default_rng(seed)
+        logits = np.empty((B, T, H, D), np.float32)
+        for b in range(B):
+            for h in range(H):
+                toks = []
+                while len(toks) < T:
+                    n = int(rng.integers(4, 25))
+                    if toks and rng.random() < 0.4 and len(toks) > n:
+                        a = int(rng.integers(0, len(toks) - n + 1))
+                        toks.extend(toks[a:a + n])
+                    else:
+                        toks.extend(rng.integers(0, 1 << D, size=n).tolist())
+                toks = np.array(toks[:T])
+                logits[b, :, h, :] = np.where((toks[:, None] >> np.arange(D)) & 1, 0.7, -0.7)
+        q = torch.from_numpy(logits).to(dt)
+        k = q.clone()
     v = nonzero_randn((B, T, Hv, Dv), seed + 2, dt)
     out_ref, insp = inspect_rosa_soft(q, k, v, max_suffix_length=W, scale=scale, dropout_p=0.0,
                                       mismatch_scale=m)
@@ -91,6 +111,35 @@ def dense_case(name, B, T, H, D, Hv, Dv, W, scale, p, m, dtype, seed, mode="rand
         dropout_seed=np.int64(dropout_seed if p > 0 else 0),
         q=f32(q), k=f32(k), v=f32(v), go=f32(go), out=f32(out),
         routes=insp.selected_route_indices.numpy().astype(np.int32),  # [B,H,T]
+        dq=f32(ql.grad), dk=f32(kl.grad), dv=f32(vl.grad),
+    )
+    print("wrote", name)
+
+
+def nonfinite_case(name):
+    """Infinities, NaN and signed zeros in every input (the policy the reference pins in
+    tests/test_soft_cuda.py:570-611): sign bits treat +0, -0 and NaN as "not positive", the
+    softsign Jacobian sends +-inf to a zero gradient and NaN to NaN."""
+    inf, nan = float("inf"), float("nan")
+    q = torch.tensor([[[[inf, -0.5]], [[0.4, -inf]], [[nan, -1.0]], [[0.0, 0.3]], [[-0.0, 0.3]],
+                       [[0.7, 0.3]], [[-0.2, 0.9]]]])
+    k = torch.tensor([[[[-1.0, inf]], [[-inf, -0.7]], [[0.2, 0.3]], [[-0.0, 0.5]], [[0.0, 0.3]],
+                       [[0.6, 0.1]], [[nan, 0.4]]]])
+    v = torch.tensor([[[[inf, -1.0]], [[-inf, 0.2]], [[0.5, -0.4]], [[0.0, nan]], [[-0.0, 1.0]],
+                       [[0.3, -0.3]], [[1.5, 0.25]]]])
+    W, scale, m = 3, 1.0, 3.0
+    out_ref, insp = inspect_rosa_soft(q, k, v, max_suffix_length=W, scale=scale, dropout_p=0.0,
+                                      mismatch_scale=m)
+    go = nonzero_randn((1, 7, 1, 2), 60, torch.float32)
+    ql, kl, vl = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out = rosa_soft.rosa_soft_reference(ql, kl, vl, max_suffix_length=W, scale=scale, mismatch_scale=m)
+    out.backward(go)
+    assert torch.equal(out.detach(), out_ref)
+    np.savez_compressed(
+        os.path.join(HERE, name + ".npz"),
+        kind="nonfinite", dtype="float32", W=W, scale=scale, p=0.0, m=m, dropout_seed=np.int64(0),
+        q=f32(q), k=f32(k), v=f32(v), go=f32(go), out=f32(out),
+        routes=insp.selected_route_indices.numpy().astype(np.int32),
         dq=f32(ql.grad), dk=f32(kl.grad), dv=f32(vl.grad),
     )
     print("wrote", name)
@@ -202,6 +251,17 @@ def main():
     dense_case("dense_f16_small", 1, 70, 4, 5, 2, 6, 9, 1.0, 0.05, 9.0, "float16", 170,
                dropout_seed=5)
     dense_case("dense_f32_t1", 2, 1, 2, 3, 1, 2, 4, 1.0, 0.0, 3.0, "float32", 180)
+    # value rows of 9..32 components (the widths of the long-match and packed benchmark
+    # configurations), narrow and wide symbols, with and without dropout and a closing window
+    dense_case("dense_f32_repeat_d2_dv16", 1, 96, 2, 2, 2, 16, 12, 1.0, 0.0, 3.0, "float32", 190,
+               mode="repeat")
+    dense_case("dense_f16_d16_dv32", 1, 72, 4, 16, 1, 32, 64, 1.0, 0.05, 9.0, "float16", 191,
+               dropout_seed=31337)
+    dense_case("dense_bf16_d20_dv24", 1, 60, 2, 20, 2, 24, 7, 1.3, 0.1, 3.0, "bfloat16", 192,
+               dropout_seed=(1 << 35) + 5)
+    dense_case("dense_f32_d8_dv12", 2, 50, 2, 8, 1, 12, 9, 0.8, 0.2, 2.0, "float32", 193,
+               dropout_seed=77)
+    nonfinite_case("nonfinite_f32_policy")
     varlen_case("varlen_f64_empty_segments", (3, 0, 5, 2), 2, 3, 1, 4, 4, 1.0, 0.25, 3.0, "float64", 200,
                 dropout_seed=(1 << 40) + 3)
     varlen_case("varlen_f32_edges", (1, 2, 127, 0, 128, 129), 2, 4, 2, 3, 160, 1.0, 0.0, 3.0,

@@ -54,3 +54,22 @@ def oracle_grads(q, k, v, go, cu, W, scale, p, m, seed, mask=7, batch_offset=0):
 def oracle_forward(q, k, v, cu, W):
     f = lambda t: t.detach().float().cpu().numpy()
     return orc.hard_forward(f(q), f(k), f(v), cu, W)
+
+
+# element-wise bound |mine - ref| <= rtol * |ref| + atol_frac * max|ref| per input dtype; the half
+# types are compared after the cast to the input dtype, with the reference's own tolerances
+CLOSE_RTOL = {"float64": 1e-4, "float32": 1e-4, "bfloat16": 2e-2, "float16": 3e-3}
+CLOSE_ATOL_FRAC = {"float64": 2e-5, "float32": 2e-5, "bfloat16": 4e-3, "float16": 1e-3}
+
+
+def assert_grads_close(mine, ref, dtype_name, label=""):
+    """allclose-style check of a float32 gradient tensor against a reference array."""
+    ref = np.asarray(ref, dtype=np.float64)
+    if dtype_name in ("bfloat16", "float16"):
+        mine = mine.to(TORCH_DTYPES[dtype_name]).float()
+    got = mine.detach().cpu().numpy().astype(np.float64).reshape(ref.shape)
+    bound = CLOSE_RTOL[dtype_name] * np.abs(ref) + CLOSE_ATOL_FRAC[dtype_name] * np.abs(ref).max()
+    excess = np.abs(got - ref) - bound
+    worst = int(np.argmax(excess))
+    assert excess.max() <= 0, (label, "element", worst, "got", got.reshape(-1)[worst], "want",
+                               ref.reshape(-1)[worst], "bound", bound.reshape(-1)[worst])

@@ -467,8 +467,10 @@ def test_route_inspection_matches_oracle_dense_and_packed():
 
 
 def test_hard_inference_with_a_horizon_beyond_the_narrow_key_range(cabi):
-    """Horizons of 2048 and more take the generic matcher (64-bit candidate keys); a copied
-    stretch of 2600 symbols makes the match length actually pass 2047."""
+    """A horizon of 2500 with one copied stretch of 2600 symbols: the match length passes 2047
+    (beyond the 11-bit length field of the narrow candidate keys).  Each row has a single genuine
+    candidate, so the hashed prefilter resolves it by walking the match backwards; the generic
+    run-length matcher is covered by the constant-stream case of test_gpu_parity_wide.py."""
     from oracle import rosa_oracle as orc
     rng = np.random.default_rng(17)
     T, H, Hp, Dp, W = 6000, 2, 1, 4, 2500

@@ -35,6 +35,19 @@ def test_workspace_sizes_are_pure_functions_of_shapes():
     assert 0 < small < large
 
 
+def test_status_word_decoding():
+    """The plan's code wins; a set tensor-core word alone reads as the timeout status."""
+    from rosa_soft_b200 import cabi
+    lib = cabi.load()
+    assert lib.rosa_b200_decode_status(0, 0) == 0
+    for code in (1, 2, 3, 4):
+        assert lib.rosa_b200_decode_status(code, 0) == code
+        assert lib.rosa_b200_decode_status(code, 1) == code
+    assert lib.rosa_b200_decode_status(0, 1) == 5      # ROSA_B200_STATUS_MMA_TIMEOUT
+    header = open(os.path.join(ROOT, "include", "rosa_soft_b200.h")).read()
+    assert re.search(r"ROSA_B200_STATUS_MMA_TIMEOUT\s*=\s*5", header)
+
+
 def test_argument_errors_without_a_gpu():
     from rosa_soft_b200 import cabi
     lib = cabi.load()
