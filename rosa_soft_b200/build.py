@@ -20,7 +20,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "librosa_soft_b200.so")
 EXT = os.path.join(PKG, "_C.so")
 
-CUDA_SOURCES = ["plan.cu", "hard_forward.cu", "hard_forward_static.cu", "surrogate_vjp.cu", "stream_runtime.cu", "api.cu"]
+CUDA_SOURCES = ["plan.cu", "hard_forward.cu", "hard_forward_static.cu", "surrogate_vjp.cu", "vjp_tiled.cu", "stream_runtime.cu", "api.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--use_fast_math", "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
@@ -44,7 +44,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
     deps = [os.path.join(CSRC, f) for f in CUDA_SOURCES] + [
         os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "bit_match.cuh"),
-        os.path.join(CSRC, "tcgen05.cuh"), os.path.join(ROOT, "include", "rosa_soft_b200.h")]
+        os.path.join(CSRC, "tcgen05.cuh"), os.path.join(CSRC, "vjp_shared.cuh"), os.path.join(ROOT, "include", "rosa_soft_b200.h")]
     if not force and _newer(LIB, deps):
         return LIB
     objdir = os.path.join(PKG, "build")

@@ -35,12 +35,11 @@
 
 #include "common.cuh"
 #include "tcgen05.cuh"
+#include "vjp_shared.cuh"
 
 namespace rosa {
 
 namespace {
-
-constexpr float kSqrtScale = 2.41421356237309504880f;  // sqrt(2) + 1
 
 // ------------------------------------------------------------ value sign bits
 template <typename T>
@@ -57,30 +56,6 @@ __global__ void pack_value_bits_kernel(const T* __restrict__ v, int64_t N, int H
   const int d0 = wd * 32, d1 = min(Dv, d0 + 32);
   for (int d = d0; d < d1; ++d) bits |= (uint32_t)((float)row[d] > 0.0f) << (d - d0);
   vbits[((int64_t)vh * N + token) * vwords + wd] = bits;
-}
-
-// ------------------------------------------------------------- item geometry
-struct Item {
-  int seq, it, h, start, len;
-  int nitems;            // items of this sequence (per head)
-  int w_begin, w_end;    // bands walked by this CTA
-  int64_t rowslot;       // first partial-row slot of this (item, head)
-  int64_t ck_base;       // first checkpoint block of this (sequence, head)
-  int64_t item_linear;   // dense index over (sequence, head, item)
-};
-
-__device__ __forceinline__ void merge_stats(float& m, float& z, float& e, float m2, float z2,
-                                            float e2) {
-  if (m2 == -CUDART_INF_F) return;
-  if (m == -CUDART_INF_F) {
-    m = m2; z = z2; e = e2;
-    return;
-  }
-  const float mm = fmaxf(m, m2);
-  const float s1 = __expf(m - mm), s2 = __expf(m2 - mm);
-  z = z * s1 + z2 * s2;
-  e = e * s1 + e2 * s2;
-  m = mm;
 }
 
 // Builds, for the rows [i0, i0 + nrows) of one head, the nibble tables
@@ -130,31 +105,6 @@ __device__ __forceinline__ float route_utility(const VjpArgs& a, const Item& it,
     }
     return u;
   }
-}
-
-// Sum of eight per-lane values across a warp in 9 shuffles instead of 40: each step
-// exchanges half of the remaining values with the partner lane.  On return every lane
-// holds the warp total of value index ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 +
-// ((lane >> 2) & 1).
-__device__ __forceinline__ float warp_reduce8(const float (&v)[8], int lane) {
-  const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
-  float a[4], b[2];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float send = h16 ? v[i] : v[i + 4];
-    const float keep = h16 ? v[i + 4] : v[i];
-    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-  }
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const float send = h8 ? a[i] : a[i + 2];
-    const float keep = h8 ? a[i + 2] : a[i];
-    b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-  }
-  float c = (h4 ? b[1] : b[0]) + __shfl_xor_sync(0xffffffffu, h4 ? b[0] : b[1], 4);
-  c += __shfl_xor_sync(0xffffffffu, c, 2);
-  c += __shfl_xor_sync(0xffffffffu, c, 1);
-  return c;
 }
 
 // ------------------------------------------------------------ block tables
@@ -228,14 +178,6 @@ __device__ __forceinline__ void fill_block_windows(const SweepSmem& sm, const It
   }
 }
 
-// Largest mismatch-count sum whose window product exp(-m * hs / D) is not flushed to zero
-// (the kernels are compiled with flush-to-zero: exp(x) == 0 for x <= -88).
-__device__ __forceinline__ int window_sum_cutoff(float neg_md) {
-  if (!(neg_md < 0.0f)) return 1000000000;
-  const float lim = -88.0f / neg_md;
-  return lim < 1.0e9f ? (int)lim : 1000000000;
-}
-
 // Forward step of one diagonal: gate, window product, evidence.  Inactive cells (before the
 // diagonal starts) leave S and hs at zero.  With kSkipDeadWindow the exponential of the window
 // product is skipped when no lane of the warp has a sum small enough to survive flush-to-zero
@@ -275,25 +217,6 @@ __device__ __forceinline__ float cell_utility(const VjpArgs& a, const Item& it,
   } else {
     return act ? route_utility<false>(a, it, vb, i, r, j + 1, ngroups, sm.ulut) : 0.0f;
   }
-}
-
-// Work item of a 1-D grid: heads vary fastest so that the longest bands of all heads are
-// scheduled first and the tail of the launch consists of the shortest bands.
-__device__ __forceinline__ bool load_item_1d(const VjpArgs& a, Item* o) {
-  const int slot = blockIdx.x / a.H;
-  if (!find_item(a.plan, slot, &o->seq, &o->it)) return false;
-  o->h = blockIdx.x - slot * a.H;
-  o->start = a.plan.seg_start[o->seq];
-  o->len = a.plan.seg_len[o->seq];
-  o->nitems = a.plan.item_prefix[o->seq + 1] - a.plan.item_prefix[o->seq];
-  const int nbands = (int)vjp_bands(o->len);
-  o->w_begin = o->it * a.bands_per_item;
-  o->w_end = min(nbands, o->w_begin + a.bands_per_item);
-  o->rowslot = a.plan.row_prefix[o->seq] * a.H +
-               ((int64_t)o->h * o->nitems + o->it) * (int64_t)o->len;
-  o->ck_base = a.plan.ck_prefix[o->seq] * a.H + (int64_t)o->h * vjp_ck_count(o->len);
-  o->item_linear = (int64_t)a.plan.item_prefix[o->seq] * a.H + (int64_t)o->h * o->nitems + o->it;
-  return true;
 }
 
 // ------------------------------------------------------------------- sweep 1
@@ -1666,6 +1589,7 @@ int launch_pack_value_bits(const void* v, int dtype, int64_t N, int Hv, int Dv, 
 int launch_vjp_sweep1(const VjpArgs& a, int items_upper, cudaStream_t stream) {
   if (items_upper <= 0) return 0;
   ProfileScope prof("vjp_sweep1", stream);
+  if (vjp_tiled_applies(a)) return launch_vjp_sweep1_tiled(a, items_upper, stream);
   const bool small_dv = a.Dv <= 32;
   const size_t bytes = sweep_common_floats(small_dv ? (a.Dv + 3) / 4 : 0) * sizeof(float);
   const unsigned grid = (unsigned)((int64_t)items_upper * a.H);

@@ -1,0 +1,433 @@
+// Register-tiled sweeps of the dense surrogate VJP (same math and schedule as
+// surrogate_vjp.cu: evidence recurrence along diagonals, online softmax with the analytic
+// reference, dropout counter, checkpoints every 16 rows).
+//
+// One thread owns FOUR consecutive diagonals and walks them down the rows together.  On block
+// row r the four cells of a thread sit on four consecutive key columns, and one row further
+// down the same four diagonals sit one column to the right, so the key-side tables (key
+// symbol, the symbol leaving the horizon window, value sign bits, first dropout hash round) of
+// a group of four rows are seven consecutive columns: two aligned 128-bit shared-memory loads
+// per table and sixteen cells, kept in registers and indexed at compile time.  Everything that
+// depends on the row only (query symbols, hash word of the query position, utility table base)
+// is loaded once per row and thread and shared by four cells; the row sums of four cells are
+// added in registers before the warp reduction.  Rows of a block always start at a multiple of
+// 16 (rows that do not exist are masked), interior blocks -- every cell active and past the
+// horizon -- run without any per-cell predicate.
+#include "common.cuh"
+#include "vjp_shared.cuh"
+
+namespace rosa {
+
+namespace {
+
+constexpr int kTR = 4;                          // diagonals per thread
+constexpr int kTBand = kVjpBand;                // diagonals per band
+constexpr int kTThreads = kTBand / kTR;         // threads per CTA
+constexpr int kTWarps = kTThreads / 32;
+constexpr int kTRows = kVjpRows;                // rows per checkpointed block
+constexpr int kTWin = kTBand + kTRows;          // window columns of a block
+static_assert(kTRows == 16 && kTBand % 128 == 0, "geometry assumed by the register windows");
+
+// Value sign bits of one route, one nibble per byte and pre-multiplied by four: byte g of the
+// result is the shared-memory word offset (times 4 bytes) of the utility-table entry of value
+// group g, so a lookup is one byte extraction and one load.
+__device__ __forceinline__ uint32_t spread_nibbles(uint32_t bits16) {
+  uint32_t out = 0;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) out |= ((bits16 >> (4 * g)) & 15u) << (8 * g + 2);
+  return out;
+}
+
+template <int kByte>
+__device__ __forceinline__ uint32_t byte_of(uint32_t w) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, 0, %2;" : "=r"(r) : "r"(w), "n"(0x4440 | kByte));
+  return r;
+}
+
+struct S1Smem {
+  int* s_k;          // [kTWin] key symbols of the column window
+  int* s_kold;       // [kTWin] key symbols W + 1 columns earlier
+  uint32_t* s_h1;    // [kTWin] first dropout hash round of route j + 1
+  uint32_t* s_vb0;   // [kTWin] spread value sign nibbles, groups 0..3
+  uint32_t* s_vb1;   // [kTWin] groups 4..7
+  int* s_q;          // [kTRows]
+  int* s_qold;       // [kTRows]
+  float* glut;       // [64] gate per mismatch count
+  float2* wstat;     // [kTRows][kTWarps] per-warp (sum e, sum e d u)
+  float* ulut;       // [kTRows][NG][16]
+};
+
+__host__ __device__ constexpr int s1_smem_words(int ng) {
+  return 5 * kTWin + 2 * kTRows + 64 + 2 * kTRows * kTWarps + kTRows * ng * 16;
+}
+
+__device__ __forceinline__ S1Smem s1_carve(float* base, int ng) {
+  S1Smem s;
+  int* w = reinterpret_cast<int*>(base);
+  s.s_k = w;                                        w += kTWin;
+  s.s_kold = w;                                     w += kTWin;
+  s.s_h1 = reinterpret_cast<uint32_t*>(w);          w += kTWin;
+  s.s_vb0 = reinterpret_cast<uint32_t*>(w);         w += kTWin;
+  s.s_vb1 = reinterpret_cast<uint32_t*>(w);         w += kTWin;
+  s.s_q = w;                                        w += kTRows;
+  s.s_qold = w;                                     w += kTRows;
+  s.glut = reinterpret_cast<float*>(w);             w += 64;
+  s.wstat = reinterpret_cast<float2*>(w);           w += 2 * kTRows * kTWarps;
+  s.ulut = reinterpret_cast<float*>(w);
+  (void)ng;
+  return s;
+}
+
+// u = gO(i) . sign(V[a]) from the nibble tables of block row r (table base `lut`)
+template <int NG>
+__device__ __forceinline__ float tiled_utility(const float* lut, uint32_t v0, uint32_t v1) {
+  const char* base = reinterpret_cast<const char*>(lut);
+  float u = *reinterpret_cast<const float*>(base + byte_of<0>(v0));
+  u += *reinterpret_cast<const float*>(base + 64 + byte_of<1>(v0));
+  if (NG > 2) {
+    u += *reinterpret_cast<const float*>(base + 128 + byte_of<2>(v0));
+    u += *reinterpret_cast<const float*>(base + 192 + byte_of<3>(v0));
+  }
+  if (NG > 4) {
+    u += *reinterpret_cast<const float*>(base + 256 + byte_of<0>(v1));
+    u += *reinterpret_cast<const float*>(base + 320 + byte_of<1>(v1));
+    u += *reinterpret_cast<const float*>(base + 384 + byte_of<2>(v1));
+    u += *reinterpret_cast<const float*>(base + 448 + byte_of<3>(v1));
+  }
+  return u;
+}
+
+// The column windows of one group of four rows: eight consecutive table entries per table,
+// cell (row rr, diagonal e) reads entry rr + 3 - e.
+template <int NG, bool kWindowed, bool kDropout>
+struct ColWindow {
+  int k[8];
+  int kold[kWindowed ? 8 : 1];
+  uint32_t h1[kDropout ? 8 : 1];
+  uint32_t v0[8];
+  uint32_t v1[NG > 4 ? 8 : 1];
+};
+
+template <int NG, bool kWindowed, bool kDropout>
+__device__ __forceinline__ void load_quad(ColWindow<NG, kWindowed, kDropout>& cw, const S1Smem& sm,
+                                          int col, int at) {
+  const int4 kq = *reinterpret_cast<const int4*>(sm.s_k + col);
+  cw.k[at] = kq.x; cw.k[at + 1] = kq.y; cw.k[at + 2] = kq.z; cw.k[at + 3] = kq.w;
+  if (kWindowed) {
+    const int4 ko = *reinterpret_cast<const int4*>(sm.s_kold + col);
+    cw.kold[at] = ko.x; cw.kold[at + 1] = ko.y; cw.kold[at + 2] = ko.z; cw.kold[at + 3] = ko.w;
+  }
+  if (kDropout) {
+    const uint4 hq = *reinterpret_cast<const uint4*>(sm.s_h1 + col);
+    cw.h1[at] = hq.x; cw.h1[at + 1] = hq.y; cw.h1[at + 2] = hq.z; cw.h1[at + 3] = hq.w;
+  }
+  const uint4 va = *reinterpret_cast<const uint4*>(sm.s_vb0 + col);
+  cw.v0[at] = va.x; cw.v0[at + 1] = va.y; cw.v0[at + 2] = va.z; cw.v0[at + 3] = va.w;
+  if (NG > 4) {
+    const uint4 vb = *reinterpret_cast<const uint4*>(sm.s_vb1 + col);
+    cw.v1[at] = vb.x; cw.v1[at + 1] = vb.y; cw.v1[at + 2] = vb.z; cw.v1[at + 3] = vb.w;
+  }
+}
+
+struct S1Params {
+  int W, hs_cut, len;
+  float neg_md, mul2, bias2;
+};
+
+// Sixteen cells: rows r0 .. r0 + 3 of the block, the thread's four diagonals.  kEdge adds the
+// predicates of blocks that touch the start of a diagonal, the first W + 1 key columns or the
+// end of the sequence.  Returns the keep flags as 16 bits (row rr, diagonal e at bit 4 rr + e)
+// and adds the row sums to es / eds.
+template <int NG, bool kWindowed, bool kDropout, bool kEdge>
+__device__ __forceinline__ uint32_t s1_group(const ColWindow<NG, kWindowed, kDropout>& cw,
+                                             const S1Smem& sm, const S1Params& p,
+                                             const DropoutKey& dkey, int r0, int i0, int j_first,
+                                             uint32_t qword0, float (&S)[kTR], int (&hs)[kTR],
+                                             float (&es)[4], float (&eds)[4]) {
+  int q[4], qo[4];
+  {
+    const int4 q4 = *reinterpret_cast<const int4*>(sm.s_q + r0);
+    q[0] = q4.x; q[1] = q4.y; q[2] = q4.z; q[3] = q4.w;
+    if (kWindowed) {
+      const int4 o4 = *reinterpret_cast<const int4*>(sm.s_qold + r0);
+      qo[0] = o4.x; qo[1] = o4.y; qo[2] = o4.z; qo[3] = o4.w;
+    }
+  }
+  // mismatch counts and the sliding window sums of all sixteen cells first: whether any window
+  // product of the warp survives flush-to-zero is decided once per group
+  int ham[4][kTR];
+  int hsv[4][kTR];
+  bool alive = false;
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr) {
+#pragma unroll
+    for (int e = 0; e < kTR; ++e) {
+      const int idx = rr + 3 - e;
+      ham[rr][e] = __popc(q[rr] ^ cw.k[idx]);
+      if (kWindowed) {
+        const int old = __popc(qo[rr] ^ cw.kold[idx]);
+        if (kEdge) {
+          const int j = j_first + rr - e;        // key column of the cell
+          const bool act = j >= 0 && i0 + r0 + rr <= p.len - 1;
+          hs[e] += (act ? ham[rr][e] : 0) - (j > p.W ? old : 0);
+          alive |= j >= p.W && hs[e] <= p.hs_cut;
+        } else {
+          hs[e] += ham[rr][e] - old;
+          alive |= hs[e] <= p.hs_cut;
+        }
+        hsv[rr][e] = hs[e];
+      }
+    }
+  }
+  float P[4][kTR];
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+    for (int e = 0; e < kTR; ++e) P[rr][e] = 0.0f;
+  if (kWindowed && __any_sync(0xffffffffu, alive)) {
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+      for (int e = 0; e < kTR; ++e) {
+        bool on = hsv[rr][e] <= p.hs_cut;
+        if (kEdge) on = on && (j_first + rr - e) >= p.W;
+        P[rr][e] = on ? __expf(p.neg_md * (float)hsv[rr][e]) : 0.0f;
+      }
+  }
+  uint32_t keepbits = 0;
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr) {
+    const float* lut = sm.ulut + (r0 + rr) * NG * 16;
+    const uint32_t qword = qword0 ^ (uint32_t)(r0 + rr);   // block rows start at a multiple of 16
+#pragma unroll
+    for (int e = 0; e < kTR; ++e) {
+      const int idx = rr + 3 - e;
+      const float x = sm.glut[ham[rr][e]];
+      const float Sn = x * (1.0f + S[e]) - P[rr][e];
+      bool act = true;
+      if (kEdge) act = (j_first + rr - e) >= 0 && i0 + r0 + rr <= p.len - 1;
+      S[e] = act ? Sn : 0.0f;
+      // the log i term cancels in the softmax, so the fixed reference drops it too
+      float ex = exp2f(fmaf(sqrtf(1.0f + S[e]), p.mul2, p.bias2));
+      if (kEdge) ex = act ? ex : 0.0f;
+      const float du = tiled_utility<NG>(lut, cw.v0[idx], NG > 4 ? cw.v1[idx] : 0u);
+      es[rr] += ex;
+      if (kDropout) {
+        const bool keep = act && dropout_keep_open(dkey, cw.h1[idx], qword);
+        keepbits |= (uint32_t)keep << (4 * rr + e);
+        eds[rr] += keep ? ex * du : 0.0f;
+      } else {
+        eds[rr] = fmaf(ex, du, eds[rr]);
+      }
+    }
+  }
+  return keepbits;
+}
+
+// Sweep 1, four diagonals per thread.  Writes the same checkpoints, keep ballots and per-item
+// row partials as vjp_sweep1_kernel<NG, true, ...> (analytic softmax reference only).
+template <int NG, bool kWindowed, bool kDropout>
+__global__ void __launch_bounds__(kTThreads) vjp_sweep1_tiled_kernel(VjpArgs a) {
+  extern __shared__ float4 smem_raw[];
+  const S1Smem sm = s1_carve(reinterpret_cast<float*>(smem_raw), NG);
+  Item it;
+  if (!load_item_1d(a, &it)) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool dense = a.plan.cu_seqlens == nullptr;
+  const int64_t sym_base = (int64_t)it.seq * a.sym_seq_stride + (int64_t)it.h * a.sym_head_stride +
+                           (dense ? 0 : it.start);
+  const int32_t* __restrict__ q = a.qsym + sym_base;
+  const int32_t* __restrict__ k = a.ksym + sym_base;
+  const int vh = it.h / a.group;
+  const uint32_t* __restrict__ vb = a.vbits + ((int64_t)vh * a.N + it.start) * a.vwords;
+  const int W = a.W;
+  S1Params p;
+  p.W = W;
+  p.len = it.len;
+  p.neg_md = -a.mismatch_scale / (float)a.D;
+  p.hs_cut = window_sum_cutoff(p.neg_md);
+  const float logit_mul = kSqrtScale * a.scale;
+  const float ref_top = a.scale * kSqrtScale * (sqrtf(1.0f + (float)W) - 1.0f);
+  p.mul2 = logit_mul * 1.4426950408889634f;
+  p.bias2 = -(logit_mul + ref_top) * 1.4426950408889634f;
+  const DropoutKey dkey = make_dropout_key((uint32_t)it.h + a.head_offset,
+                                           (uint32_t)it.seq + a.batch_offset, a.seed, a.dropout_p);
+  if (tid <= a.D) sm.glut[tid] = expf(p.neg_md * (float)tid);
+  const int vslot = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+
+  for (int w = it.w_begin; w < it.w_end; ++w) {
+    const int dmin = 1 + w * kTBand;
+    const int dmax = dmin + kTBand - 1;
+    float S[kTR];
+    int hs[kTR];
+#pragma unroll
+    for (int e = 0; e < kTR; ++e) {
+      S[e] = 0.0f;
+      hs[e] = 0;
+    }
+    const int rb_lo = dmin / kTRows, rb_hi = (it.len - 1) / kTRows;
+    const int64_t ck_band = it.ck_base + vjp_ck_before(it.len, w);
+    for (int rb = rb_lo; rb <= rb_hi; ++rb) {
+      const int i0 = rb * kTRows;                 // rows i0 .. i0 + 15, masked where absent
+      const int jwin0 = i0 - dmax;                // key column of window index 0
+      const int first_row = max(i0, dmin);        // rows below it belong to no cell of the band
+      const int skew = first_row - i0;
+      const int64_t ck_idx = ck_band + (rb - rb_lo);
+      __syncthreads();
+      // ---- block tables
+      for (int c = tid; c < kTWin; c += kTThreads) {
+        const int j = jwin0 + c;
+        const bool in = j >= 0 && j < it.len - 1;
+        sm.s_k[c] = in ? __ldg(k + j) : 0;
+        const int jo = j - W - 1;
+        sm.s_kold[c] = (kWindowed && jo >= 0 && jo < it.len) ? __ldg(k + jo) : 0;
+        if (kDropout) sm.s_h1[c] = dropout_route_open((uint32_t)(j + 1));
+        const uint32_t bits = in ? __ldg(vb + j + 1) : 0u;
+        sm.s_vb0[c] = spread_nibbles(bits & 0xffffu);
+        if (NG > 4) sm.s_vb1[c] = spread_nibbles(bits >> 16);
+      }
+      if (tid < kTRows) {
+        const int i = i0 + tid;
+        const bool in = i >= first_row && i <= it.len - 1;
+        sm.s_q[tid] = in ? __ldg(q + i) : 0;
+        sm.s_qold[tid] = (kWindowed && in && i - W - 1 >= 0) ? __ldg(q + i - W - 1) : 0;
+      }
+      // nibble tables: one thread per (row, value group) builds its sixteen signed sums
+      for (int e = tid; e < kTRows * NG; e += kTThreads) {
+        const int r = e / NG, g = e - r * NG;
+        const int i = i0 + r;
+        float gv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (i >= first_row && i <= it.len - 1) {
+          const int64_t base = (((int64_t)it.start + i) * a.H + it.h) * a.Dv + 4 * g;
+#pragma unroll
+          for (int b = 0; b < 4; ++b)
+            if (4 * g + b < a.Dv) gv[b] = load_as_float(a.go, base + b, a.dtype);
+        }
+        float4* dst = reinterpret_cast<float4*>(sm.ulut + e * 16);
+#pragma unroll
+        for (int n4 = 0; n4 < 4; ++n4) {
+          // nibbles 4 n4 .. 4 n4 + 3: bits 2 and 3 fixed by n4, bits 0 and 1 vary
+          const float hi = ((n4 & 1) ? gv[2] : -gv[2]) + ((n4 & 2) ? gv[3] : -gv[3]);
+          dst[n4] = make_float4(hi - gv[0] - gv[1], hi + gv[0] - gv[1], hi - gv[0] + gv[1],
+                                hi + gv[0] + gv[1]);
+        }
+      }
+      __syncthreads();
+      // ---- checkpoint of the thread's four diagonals
+      {
+        int4* ck = reinterpret_cast<int4*>(a.ckpt + ck_idx * kTBand + kTR * tid);
+        ck[0] = make_int4(__float_as_int(S[0]), hs[0], __float_as_int(S[1]), hs[1]);
+        ck[1] = make_int4(__float_as_int(S[2]), hs[2], __float_as_int(S[3]), hs[3]);
+      }
+      const bool interior = jwin0 >= (kWindowed ? W + 1 : 0) && i0 + kTRows - 1 <= it.len - 1;
+      const uint32_t qword0 = dropout_query_word((uint32_t)i0);
+      // window column of (row 0, diagonal 3 of this thread); a multiple of 4
+      const int col0 = kTBand - kTR - kTR * tid;
+      ColWindow<NG, kWindowed, kDropout> cw;
+      load_quad<NG, kWindowed, kDropout>(cw, sm, col0, 0);
+      uint32_t* keep_out = a.keepbits + (ck_idx * kTRows) * kVjpWarps;
+#pragma unroll 1
+      for (int r0 = 0; r0 < kTRows; r0 += 4) {
+        load_quad<NG, kWindowed, kDropout>(cw, sm, col0 + r0 + 4 < kTWin ? col0 + r0 + 4 : col0 + r0, 4);
+        float es[4] = {0.0f, 0.0f, 0.0f, 0.0f}, eds[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // key column of (row r0, diagonal 0 of this thread)
+        const int j_first = jwin0 + col0 + r0 + 3;
+        uint32_t keep;
+        if (interior)
+          keep = s1_group<NG, kWindowed, kDropout, false>(cw, sm, p, dkey, r0, i0, j_first, qword0, S,
+                                                          hs, es, eds);
+        else
+          keep = s1_group<NG, kWindowed, kDropout, true>(cw, sm, p, dkey, r0, i0, j_first, qword0, S,
+                                                         hs, es, eds);
+        if (kDropout) {
+          // keep ballots in the layout of the one-diagonal-per-thread kernels: one word per row
+          // and 32 diagonals, i.e. the nibbles of eight neighbouring threads
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            uint32_t word = ((keep >> (4 * rr)) & 15u) << (4 * (lane & 7));
+            word |= __shfl_xor_sync(0xffffffffu, word, 1);
+            word |= __shfl_xor_sync(0xffffffffu, word, 2);
+            word |= __shfl_xor_sync(0xffffffffu, word, 4);
+            const int r = r0 + rr;
+            if ((lane & 7) == 0 && r >= skew && i0 + r <= it.len - 1)
+              keep_out[(r - skew) * kVjpWarps + (tid >> 3)] = word;
+          }
+        }
+        float v[8];
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) {
+          v[2 * rr] = es[rr];
+          v[2 * rr + 1] = eds[rr];
+        }
+        const float total = warp_reduce8(v, lane);
+        if ((lane & 3) == 0)
+          reinterpret_cast<float*>(sm.wstat + (r0 + (vslot >> 1)) * kTWarps + warp)[vslot & 1] = total;
+        // the upper quad becomes the lower one of the next group
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          cw.k[x] = cw.k[x + 4];
+          if (kWindowed) cw.kold[x] = cw.kold[x + 4];
+          if (kDropout) cw.h1[x] = cw.h1[x + 4];
+          cw.v0[x] = cw.v0[x + 4];
+          if (NG > 4) cw.v1[x] = cw.v1[x + 4];
+        }
+      }
+      __syncthreads();
+      if (tid < kTRows) {
+        const int i = i0 + tid;
+        if (i >= first_row && i <= it.len - 1) {
+          float m = ref_top - logf((float)i), z = 0.0f, e = 0.0f;
+#pragma unroll
+          for (int ww = 0; ww < kTWarps; ++ww) {
+            const float2 part = sm.wstat[tid * kTWarps + ww];
+            z += part.x;
+            e += part.y;
+          }
+          e *= a.inv_keep;
+          const int64_t slot = it.rowslot + i;
+          if (w > it.w_begin) {
+            const float4 prev = a.stat_part[slot];
+            merge_stats(m, z, e, prev.x, prev.y, prev.z);
+          }
+          a.stat_part[slot] = make_float4(m, z, e, 0.0f);
+        }
+      }
+    }
+  }
+}
+
+template <int NG>
+int launch_s1_tiled(const VjpArgs& a, unsigned grid, cudaStream_t stream) {
+  const size_t smem = (size_t)s1_smem_words(NG) * sizeof(float);
+  const bool windowed = a.ring_slots > 0;
+  const bool dropout = a.dropout_p > 0.0f;
+  if (windowed && dropout)
+    vjp_sweep1_tiled_kernel<NG, true, true><<<grid, kTThreads, smem, stream>>>(a);
+  else if (windowed)
+    vjp_sweep1_tiled_kernel<NG, true, false><<<grid, kTThreads, smem, stream>>>(a);
+  else if (dropout)
+    vjp_sweep1_tiled_kernel<NG, false, true><<<grid, kTThreads, smem, stream>>>(a);
+  else
+    vjp_sweep1_tiled_kernel<NG, false, false><<<grid, kTThreads, smem, stream>>>(a);
+  ROSA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace
+
+bool vjp_tiled_applies(const VjpArgs& a) {
+  // value rows of up to 32 components (nibble tables), the analytic softmax reference, and not
+  // the testing flag that selects the one-diagonal-per-thread kernels
+  const float top = a.scale * kSqrtScale * (sqrtf(1.0f + (float)a.W) - 1.0f);
+  return a.Dv <= 32 && top <= 80.0f && !a.force_cuda_core_contraction;
+}
+
+int launch_vjp_sweep1_tiled(const VjpArgs& a, int items_upper, cudaStream_t stream) {
+  const unsigned grid = (unsigned)((int64_t)items_upper * a.H);
+  if (a.Dv <= 8) return launch_s1_tiled<2>(a, grid, stream);
+  if (a.Dv <= 16) return launch_s1_tiled<4>(a, grid, stream);
+  return launch_s1_tiled<8>(a, grid, stream);
+}
+
+}  // namespace rosa

@@ -10,8 +10,34 @@ for the computation; callers that want the full tensors back gather them afterwa
 """
 from __future__ import annotations
 
+import contextlib
+import threading
 from dataclasses import dataclass
 from typing import List, Sequence, Tuple
+
+_coordinates = threading.local()
+
+
+def current_dropout_coordinates() -> Tuple[int, int]:
+    """(batch_offset, head_offset) that the public operators record for their backward."""
+    return getattr(_coordinates, "value", (0, 0))
+
+
+@contextlib.contextmanager
+def dropout_coordinates(batch_offset: int = 0, head_offset: int = 0):
+    """Calls of ``rosa_soft`` / ``rosa_soft_varlen`` made inside this context belong to a shard
+    whose first sequence and first query head have these global indices: the backward adds them
+    to the dropout counter's batch and head words, so the shard draws the masks of the unsharded
+    run (reference convention: rosa_soft/soft_reference.py:394-447).  The offsets are captured
+    when the forward runs; the backward may run after the context has been left."""
+    if batch_offset < 0 or head_offset < 0:
+        raise ValueError("shard offsets must be non-negative")
+    previous = current_dropout_coordinates()
+    _coordinates.value = (int(batch_offset), int(head_offset))
+    try:
+        yield
+    finally:
+        _coordinates.value = previous
 
 
 @dataclass(frozen=True)
@@ -63,6 +89,26 @@ def balance_sequences(lengths: Sequence[int], world: int) -> List[List[int]]:
         loads[rank] += lengths[ordinal] * lengths[ordinal]
         owned[rank].append(ordinal)
     return [sorted(o) for o in owned]
+
+
+def packed_shard_offsets(lengths: Sequence[int], owned: Sequence[int]) -> Tuple[List[int], List[int]]:
+    """Offsets and token ranges of one rank's share of a packed batch.  The rank keeps EVERY
+    sequence ordinal in its ``cu_seqlens`` (the ones it does not own have length zero), because
+    the dropout counter's batch word is the sequence ordinal counting empty sequences
+    (reference rosa_soft/soft_reference.py:683-699): the shard then needs no offset at all.
+    Returns (cu_seqlens of the shard, [start, stop) token ranges of the owned sequences in the
+    full packed batch, in ordinal order)."""
+    owned_set = set(owned)
+    starts = [0]
+    for n in lengths:
+        starts.append(starts[-1] + n)
+    cu, ranges = [0], []
+    for ordinal, n in enumerate(lengths):
+        take = n if ordinal in owned_set else 0
+        cu.append(cu[-1] + take)
+        if take:
+            ranges.append((starts[ordinal], starts[ordinal + 1]))
+    return cu, ranges
 
 
 def max_over_ranks(local_ms: float, group=None) -> float:

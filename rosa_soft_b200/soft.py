@@ -18,6 +18,7 @@ from torch import Tensor
 from torch.autograd.function import once_differentiable
 
 from . import soft_contract as _contract
+from .sharding import current_dropout_coordinates as _shard_coordinates
 from .soft_contract import (  # noqa: F401  (re-exported like the reference module does)
     ROSA_SOFT_DEFAULT_DROPOUT_P,
     ROSA_SOFT_DEFAULT_MISMATCH_SCALE,
@@ -59,6 +60,10 @@ def _fake_vjp(query, key, value, *rest):
     )
 
 
+def _fake_vjp_sharded(query, key, value, cu_seqlens, *rest):
+    return _fake_vjp(query, key, value, *rest[:-2])
+
+
 def _fake_inference(query_symbols, key_symbols, payload, cu_seqlens, max_suffix_length):
     return (payload.new_empty((*query_symbols.shape, payload.shape[-1])),
             query_symbols.new_empty(query_symbols.shape, dtype=torch.int64))
@@ -69,6 +74,7 @@ for _name, _fake in (
     ("hard_forward_varlen", _fake_forward(dense=False)),
     ("surrogate_vjp_masked", _fake_vjp),
     ("surrogate_vjp_varlen_masked", _fake_vjp),
+    ("surrogate_vjp_sharded", _fake_vjp_sharded),
     ("hard_inference", _fake_inference),
 ):
     torch.library.register_fake(f"rosa_soft::{_name}")(_fake)
@@ -91,6 +97,7 @@ class _HardForwardSoftVjp(torch.autograd.Function):
                                                                   horizon)
             ctx.save_for_backward(query, key, value, packed_q, packed_k, dropout_seed, cu_seqlens)
         ctx.controls = (horizon, float(scale), float(dropout_p), float(mismatch_scale))
+        ctx.shard = _shard_coordinates()   # (0, 0) unless inside sharding.dropout_coordinates
         return output
 
     @staticmethod
@@ -99,7 +106,12 @@ class _HardForwardSoftVjp(torch.autograd.Function):
         query, key, value, packed_q, packed_k, dropout_seed, *offsets = ctx.saved_tensors
         wanted = ctx.needs_input_grad[:3]
         mask = sum(bit for bit, need in zip((1, 2, 4), wanted) if need)
-        if offsets:
+        if ctx.shard != (0, 0):
+            gradients = _OPS.surrogate_vjp_sharded(query, key, value,
+                                                   offsets[0] if offsets else None, grad_output,
+                                                   packed_q, packed_k, dropout_seed,
+                                                   *ctx.controls, mask, *ctx.shard)
+        elif offsets:
             gradients = _OPS.surrogate_vjp_varlen_masked(query, key, value, offsets[0], grad_output,
                                                          packed_q, packed_k, dropout_seed,
                                                          *ctx.controls, mask)

@@ -97,10 +97,13 @@ def test_value_widths_and_symbol_widths_against_oracle(cabi, shape):
 
 
 def test_long_match_stress_full_length_against_oracle(cabi):
-    """T = 8192, D = 2, Dv = 16, W = 256, bf16, repeated segments of 16..256 tokens: two whole
-    (batch, head) slices of the configuration against the float64 oracle."""
+    """T = 8192, D = 2, Dv = 16, W = 256, bf16: whole (batch, head) slices against the float64
+    oracle.  Head 0 is the benchmark's stream (repeated segments of 16..256 tokens: matches of up
+    to 255 symbols); head 1 repeats segments of up to 700 tokens, so matches sit on the horizon for
+    hundreds of rows and the window products of the adjoint stay alive (the cancellation regime)."""
     T, H, D, Hv, Dv, W = 8192, 2, 2, 2, 16, 256
-    q = repeated_stream_logits(T, H, D, seed=1003, repeat_prob=0.3, seg=(16, 256))
+    q = torch.cat([repeated_stream_logits(T, 1, D, seed=1003, repeat_prob=0.3, seg=(16, 256)),
+                   repeated_stream_logits(T, 1, D, seed=1004, repeat_prob=0.4, seg=(16, 700))], dim=1)
     q = q.to(torch.bfloat16).to(DEV)
     k = q.clone()
     v = nonzero_randn((T, Hv, Dv), 7, torch.bfloat16).to(DEV)
@@ -112,11 +115,14 @@ def test_long_match_stress_full_length_against_oracle(cabi):
     assert np.array_equal(routes.cpu().numpy(), np.where(ref_route > 0, ref_route, -1))
     _, ref_len = orc.hard_routes(orc.pack_symbols(q.float().cpu().numpy()),
                                  orc.pack_symbols(k.float().cpu().numpy()), cu, W)
-    assert (ref_len == W).mean() > 0.01          # matches really sit on the horizon
+    assert (ref_len[:, 0] >= 128).mean() > 0.05   # long matches in the benchmark's stream
+    assert (ref_len[:, 1] == W).mean() > 0.05     # and matches that sit on the horizon
     rq, rk, rv = oracle_grads(q, k, v, go, cu, W, 1.0, 0.0, 3.0, 0)
     for name, mine, ref in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
-        err = normalised_error(mine.cpu().numpy(), ref)
-        assert err <= GRAD_TOL, (name, err)
+        for h in range(H):
+            hv = slice(h, h + 1)
+            err = normalised_error(mine[:, hv].cpu().numpy(), ref[:, hv])
+            assert err <= GRAD_TOL, (name, h, err)
 
 
 def test_packed_configuration_sequences_against_oracle(cabi):
@@ -158,25 +164,32 @@ def test_packed_configuration_sequences_against_oracle(cabi):
 
 # ------------------------------------------------------------------ fall-back matchers
 
-def _periodic_symbols(T, H, period, bits, seed):
+def _two_symbol_stream(T, H, bits, seed):
+    """Random stream over two symbols of `bits` bits: about half of the earlier positions agree
+    with a row's last symbol (genuine candidates by the thousand), yet matches stay a dozen
+    symbols long, so no row ever stops early on a match at the horizon."""
     rng = np.random.default_rng(seed)
-    base = rng.integers(0, 1 << bits, size=(period, H), dtype=np.uint64).astype(np.uint32)
-    return np.tile(base, ((T + period - 1) // period, 1))[:T]
+    pair = rng.integers(1 << (bits - 1), 1 << bits, size=(2, H), dtype=np.uint64).astype(np.uint32)
+    pick = rng.integers(0, 2, size=(T, H))
+    return np.where(pick == 1, pair[1][None, :], pair[0][None, :]).astype(np.uint32)
 
 
 def test_wide_symbol_rows_beyond_the_prefilter_limit_take_the_run_length_matcher(cabi):
-    """Constant and short-period streams of 32-bit symbols give every row hundreds of genuine
-    candidates: the hashed prefilter raises its flag, the run-length matcher redoes the launch
-    and merges into the rows the prefilter had already resolved."""
-    T, H, Hp, Dp, W = 2600, 3, 1, 2, 50
-    k = _periodic_symbols(T, H, 7, 32, 5)
-    k[:, 1] = 0xDEADBEEF                      # a constant stream
+    """Streams of 32-bit symbols over a two-symbol alphabet give every late row thousands of
+    genuine candidates: the hashed prefilter raises its flag, the run-length matcher redoes the
+    launch and merges into the rows the prefilter had already resolved (a random wide-symbol head
+    and a short sequence stay with the prefilter)."""
+    T, H, Hp, Dp, W = 6200, 3, 1, 2, 50
+    k = _two_symbol_stream(T, H, 32, 5)
     rng = np.random.default_rng(6)
-    k[:, 2] = rng.integers(0, 1 << 32, size=T, dtype=np.uint64).astype(np.uint32)   # a random one
-    q = k.copy()
-    q[1:] = k[:-1]                            # the query repeats the previous key: long matches
+    k[:, 2] = rng.integers(0, 1 << 32, size=T, dtype=np.uint64).astype(np.uint32)   # a random head
+    # the query stream is drawn independently over the same two symbols (a shifted copy of the
+    # keys would match at the horizon on every row and stop the prefilter at once)
+    pick = rng.integers(0, 2, size=(T, H))
+    q = np.where(pick == 1, k.max(axis=0)[None, :], k.min(axis=0)[None, :]).astype(np.uint32)
+    q[:, 2] = k[:, 2]
     pay = rng.standard_normal((T, Hp, Dp)).astype(np.float32)
-    cu_np = np.array([0, 1000, 1000, T], dtype=np.int64)
+    cu_np = np.array([0, 300, 300, T], dtype=np.int64)
     ref_out, ref_end = orc.hard_inference(q, k, pay, cu_np, W)
     out, end, ws = cabi.hard_inference(torch.from_numpy(q.view(np.int32)).to(DEV),
                                        torch.from_numpy(k.view(np.int32)).to(DEV),
@@ -186,15 +199,14 @@ def test_wide_symbol_rows_beyond_the_prefilter_limit_take_the_run_length_matcher
     assert np.array_equal(out.cpu().numpy(), ref_out)
     assert cabi.read_status(ws) == 0
     # the flag word of the plan says that the fall-back really ran
-    flag = ws[:16].view(torch.int32).cpu().numpy()
-    assert flag[2] == 1
+    assert ws[:16].view(torch.int32).cpu().numpy()[2] == 1
 
 
-def test_training_forward_with_wide_periodic_symbols(cabi):
-    """The training forward with D = 12 (hashed prefilter) on a short-period stream: same
+def test_training_forward_with_wide_two_symbol_stream(cabi):
+    """The training forward with D = 12 (hashed prefilter) on a two-symbol stream: same
     fall-back, checked through the operator's outputs."""
-    T, H, D, Hv, Dv, W = 1500, 2, 12, 1, 4, 64
-    sym = _periodic_symbols(T, H, 5, D, 9)
+    T, H, D, Hv, Dv, W = 6200, 2, 12, 1, 4, 64
+    sym = _two_symbol_stream(T, H, D, 9)
     bits = (sym[..., None] >> np.arange(D)) & 1
     q = torch.from_numpy(np.where(bits, 0.6, -0.6).astype(np.float32)).to(DEV)
     k = q.clone()
@@ -207,12 +219,15 @@ def test_training_forward_with_wide_periodic_symbols(cabi):
 
 
 def test_horizon_beyond_the_narrow_key_range_takes_the_generic_matcher(cabi):
-    """W >= 2048 on a constant stream: the prefilter gives up and the generic run-length matcher
-    (64-bit candidate keys) resolves match lengths up to the horizon of 2500."""
-    T, H, W = 5200, 2, 2500
-    k = np.full((T, H), 0x01020304, np.uint32)
-    k[:, 1] = _periodic_symbols(T, 1, 3, 32, 4)[:, 0]
-    q = k.copy()
+    """W >= 2048: a constant stretch of 3000 symbols (matches up to the horizon of 2500) followed
+    by a two-symbol stream whose rows overflow the prefilter: the generic run-length matcher
+    (64-bit candidate keys) redoes the launch."""
+    T, H, W = 7400, 2, 2500
+    k = _two_symbol_stream(T, H, 32, 4)
+    k[:3000] = k[0]                            # constant start: one of the two symbols per head
+    q = _two_symbol_stream(T, H, 32, 4)        # same alphabet (same seed), then reshuffled
+    q = q[np.random.default_rng(11).permutation(T)]
+    q[:3000] = k[:3000]
     pay = np.random.default_rng(8).standard_normal((T, 1, 2)).astype(np.float32)
     cu_np = np.array([0, T], dtype=np.int64)
     ref_out, ref_end = orc.hard_inference(q, k, pay, cu_np, W)

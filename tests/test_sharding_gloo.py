@@ -81,3 +81,35 @@ def test_shard_bookkeeping():
     assert sorted(sum(owned, [])) == list(range(6))
     loads = [sum(l * l for l in ([4096, 64, 3000, 3000, 100, 2048][s] for s in o)) for o in owned]
     assert max(loads) / min(loads) < 1.3
+
+
+def test_packed_shards_keep_every_sequence_ordinal():
+    """A rank's cu_seqlens names all sequences (foreign ones empty), so the sequence ordinal --
+    the dropout counter's batch word for packed batches -- needs no offset: the oracle on the
+    two shares reproduces the unsharded packed gradients bit for bit."""
+    from oracle import rosa_oracle as orc
+    from rosa_soft_b200 import sharding
+
+    lengths = [20, 0, 33, 5, 27]
+    N, H, D, Hv, Dv, W = sum(lengths), 2, 3, 1, 4, 6
+    rng = np.random.default_rng(4)
+    q, k = rng.standard_normal((N, H, D)), rng.standard_normal((N, H, D))
+    v, go = rng.standard_normal((N, Hv, Dv)), rng.standard_normal((N, H, Dv))
+    cu_full = np.concatenate([[0], np.cumsum(lengths)])
+    full = orc.surrogate_vjp(q, k, v, go, cu_full, W, 1.0, 0.4, 3.0, seed=5)
+    owned = sharding.balance_sequences(lengths, 2)
+    seen = np.zeros(N, bool)
+    for rank in range(2):
+        cu, ranges = sharding.packed_shard_offsets(lengths, owned[rank])
+        assert len(cu) == len(lengths) + 1 and cu[-1] == sum(lengths[s] for s in owned[rank])
+        idx = np.concatenate([np.arange(a, b) for a, b in ranges])
+        assert not seen[idx].any()
+        seen[idx] = True
+        part = orc.surrogate_vjp(q[idx], k[idx], v[idx], go[idx], np.array(cu), W, 1.0, 0.4, 3.0,
+                                 seed=5)
+        for mine, want in zip(part, full):
+            assert np.array_equal(mine, want[idx])
+    assert seen.all()
+    with sharding.dropout_coordinates(3, 8):
+        assert sharding.current_dropout_coordinates() == (3, 8)
+    assert sharding.current_dropout_coordinates() == (0, 0)
