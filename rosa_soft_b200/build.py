@@ -20,7 +20,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "librosa_soft_b200.so")
 EXT = os.path.join(PKG, "_C.so")
 
-CUDA_SOURCES = ["plan.cu", "hard_forward.cu", "hard_forward_static.cu", "surrogate_vjp.cu", "vjp_tiled.cu", "stream_runtime.cu", "api.cu"]
+CUDA_SOURCES = ["plan.cu", "hard_forward.cu", "hard_forward_static.cu", "surrogate_vjp.cu", "vjp_tiled.cu", "vjp_tiled_sweep2.cu", "stream_runtime.cu", "api.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--use_fast_math", "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",

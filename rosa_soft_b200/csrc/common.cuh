@@ -359,6 +359,7 @@ int launch_vjp_sweep1(const VjpArgs& a, int items_upper, cudaStream_t stream);
 // register-tiled sweeps (vjp_tiled.cu): four diagonals per thread
 bool vjp_tiled_applies(const VjpArgs& a);
 int launch_vjp_sweep1_tiled(const VjpArgs& a, int items_upper, cudaStream_t stream);
+int launch_vjp_sweep2_tiled(const VjpArgs& a, int items_upper, cudaStream_t stream);
 int launch_vjp_rowstats(const VjpArgs& a, cudaStream_t stream);
 int launch_vjp_sweep2(const VjpArgs& a, int items_upper, cudaStream_t stream);
 int launch_vjp_finalize(const VjpArgs& a, cudaStream_t stream);

@@ -1636,6 +1636,7 @@ int launch_vjp_rowstats(const VjpArgs& a, cudaStream_t stream) {
 int launch_vjp_sweep2(const VjpArgs& a, int items_upper, cudaStream_t stream) {
   if (items_upper <= 0) return 0;
   ProfileScope prof("vjp_sweep2", stream);
+  if (vjp_tiled_applies(a)) return launch_vjp_sweep2_tiled(a, items_upper, stream);
   if (a.Dv <= 32 && !a.force_cuda_core_contraction) {
     // tensor-core contraction (tcgen05): operand N is 16 or 32 for both symbol and value dims
     if (a.D <= 16) return launch_sweep2_tc<16>(a, items_upper, stream);

@@ -135,7 +135,7 @@ __device__ __forceinline__ uint32_t s1_group(const ColWindow<NG, kWindowed, kDro
         if (kEdge) {
           const int j = j_first + rr - e;        // key column of the cell
           const bool act = j >= 0 && i0 + r0 + rr <= p.len - 1;
-          hs[e] += (act ? ham[rr][e] : 0) - (j > p.W ? old : 0);
+          hs[e] += act ? ham[rr][e] - (j > p.W ? old : 0) : 0;
           alive |= j >= p.W && hs[e] <= p.hs_cut;
         } else {
           hs[e] += ham[rr][e] - old;
@@ -382,10 +382,11 @@ int launch_s1_tiled(const VjpArgs& a, unsigned grid, cudaStream_t stream) {
 }  // namespace
 
 bool vjp_tiled_applies(const VjpArgs& a) {
-  // value rows of up to 32 components (nibble tables), the analytic softmax reference, and not
-  // the testing flag that selects the one-diagonal-per-thread kernels
+  // value rows of up to 32 components (nibble tables), symbols of up to 16 bits (one MMA N of the
+  // second sweep), the analytic softmax reference, and not the testing flag that selects the
+  // one-diagonal-per-thread kernels
   const float top = a.scale * kSqrtScale * (sqrtf(1.0f + (float)a.W) - 1.0f);
-  return a.Dv <= 32 && top <= 80.0f && !a.force_cuda_core_contraction;
+  return a.Dv <= 32 && a.D <= 16 && top <= 80.0f && !a.force_cuda_core_contraction;
 }
 
 int launch_vjp_sweep1_tiled(const VjpArgs& a, int items_upper, cudaStream_t stream) {

@@ -1,0 +1,872 @@
+// Second sweep of the dense surrogate VJP, register-tiled: the same schedule and tensor-core
+// contraction as vjp_sweep2_tc_kernel (surrogate_vjp.cu) with TWO consecutive diagonals per
+// thread and 128 threads per band of 256 diagonals.
+//
+// Per row block (16 rows, bottom-up): the forward recurrence is re-run from the block's
+// checkpoint (evidence S kept in a thread-private shared-memory column, the mismatch counts
+// packed into bytes), the adjoint recurrence runs backwards over it and writes the cell adjoint
+// C and the weighted probability p*d as bf16 terms into one un-skewed [row][window column]
+// operand area, and tcgen05.mma contracts that area three ways (column sums C^T qz and
+// (p d)^T gO, row sums C kz) into fp32 accumulators in tensor memory.  The MMAs of block b run
+// while the tables and the forward phase of block b+1 are computed; their accumulators are
+// added to the CTA-owned partial gradient rows just before block b+1 overwrites the operands.
+//
+// What the two-diagonal tiling buys: key-side tables of four rows are six consecutive columns
+// held in registers (64-bit shared loads), row-only values are loaded once for two cells, on
+// even rows the two cells of a thread are one aligned 32-bit operand store per term, S and the
+// packed mismatch counts move as 64-bit words, and blocks whose cells are all active and past
+// the horizon run without per-cell predicates.
+//
+// Operand precision follows the input dtype: float32 inputs keep three bf16 terms of C (24
+// mantissa bits, the row sums cancel heavily) and two of p*d; float16 inputs two and two;
+// bfloat16 inputs two terms of C and one of p*d -- their gradients are compared at the half
+// precision tolerances of the operator contract (3e-3 / 2e-2), far above what is dropped.
+#include "common.cuh"
+#include "tcgen05.cuh"
+#include "vjp_shared.cuh"
+#include "vjp_tiled.cuh"
+
+namespace rosa {
+
+namespace {
+
+constexpr int kS2Threads = 128;
+constexpr int kS2R = 2;                              // diagonals per thread
+constexpr int kS2Band = kVjpBand;                    // 256 diagonals per band
+constexpr int kS2Rows = kVjpRows;                    // 16
+constexpr int kS2Win = kS2Band + kS2Rows;            // 272 window columns
+constexpr int kS2NK = 16;                            // symbol bits padded to one MMA N
+static_assert(kS2Threads * kS2R == kS2Band && kS2Rows == 16, "tile geometry");
+
+// Operand area: core matrices of 8 rows x 16 bytes, ordered [column group][term][row group],
+// 144 bytes apart inside a term (128 + 16 of skew), terms 288 bytes apart, column groups
+// NT * 288 + 16 bytes apart (an odd multiple of 16, so that the 32-bit stores of a warp -- 8
+// column groups, 4 lanes per 16-byte core row -- fall into 32 different banks).
+constexpr int kRowGroupBytes = 144;
+constexpr int kTermBytes = 2 * kRowGroupBytes;
+__host__ __device__ constexpr int col_group_bytes(int nterms) { return nterms * kTermBytes + 16; }
+__host__ __device__ constexpr int operand_bytes(int nterms) {
+  // the K-major view with M = 64 reads eight cores (1152 bytes) from every column group start:
+  // keep that much readable after the last group
+  return (kS2Win / 8) * col_group_bytes(nterms) + 8 * kRowGroupBytes;
+}
+__host__ __device__ constexpr int chunk_start(int ch) {
+  return ch == 0 ? 0 : ch == 1 ? 128 : kS2Win - 128;
+}
+// B operand tiles, K-major: element (n, k) of an N x K matrix
+__device__ __forceinline__ int b_off(int n, int k, int N) {
+  return (k >> 3) * (N / 8 * 128) + (n >> 3) * 128 + (n & 7) * 16 + (k & 7) * 2;
+}
+
+// precision policy per input dtype
+template <int kPrec> struct Terms;               // 0 float32, 1 float16, 2 bfloat16
+template <> struct Terms<0> { static constexpr int C = 3, P = 2; static constexpr bool glo = true; };
+template <> struct Terms<1> { static constexpr int C = 2, P = 2; static constexpr bool glo = true; };
+template <> struct Terms<2> { static constexpr int C = 2, P = 1; static constexpr bool glo = false; };
+
+__device__ __forceinline__ uint32_t hi_bits(float v) { return __float_as_uint(v) & 0xffff0000u; }
+// (upper half of b) << 16 | upper half of a
+__device__ __forceinline__ uint32_t pack_hi(uint32_t a, uint32_t b) {
+  return __byte_perm(a, b, 0x7632);
+}
+__device__ __forceinline__ uint32_t pack_rn(float a, float b) {   // bf16(b) << 16 | bf16(a)
+  const __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&p);
+}
+
+// Splits two neighbouring cells (column c: lo half, column c + 1: hi half) into NT bf16 terms.
+// kRound = false: the leading terms by truncation (one mask each; their remainder is exact in
+// float32), the last by rounding.  kRound = true (float32 inputs): every term rounded to nearest,
+// which halves the representation error of the last term.
+template <int NT, bool kRound>
+__device__ __forceinline__ void split_pair(float a, float b, uint32_t (&out)[3]) {
+  if (NT == 1) {
+    out[0] = pack_rn(a, b);
+    return;
+  }
+  float ra, rb;
+  if (kRound) {
+    out[0] = pack_rn(a, b);
+    ra = a - __uint_as_float(out[0] << 16);
+    rb = b - __uint_as_float(out[0] & 0xffff0000u);
+  } else {
+    const uint32_t a0 = hi_bits(a), b0 = hi_bits(b);
+    out[0] = pack_hi(a0, b0);
+    ra = a - __uint_as_float(a0);
+    rb = b - __uint_as_float(b0);
+  }
+  if (NT == 2) {
+    out[1] = pack_rn(ra, rb);
+    return;
+  }
+  float sa, sb2;
+  if (kRound) {
+    out[1] = pack_rn(ra, rb);
+    sa = ra - __uint_as_float(out[1] << 16);
+    sb2 = rb - __uint_as_float(out[1] & 0xffff0000u);
+  } else {
+    const uint32_t a1 = hi_bits(ra), b1 = hi_bits(rb);
+    out[1] = pack_hi(a1, b1);
+    sa = ra - __uint_as_float(a1);
+    sb2 = rb - __uint_as_float(b1);
+  }
+  out[2] = pack_rn(sa, sb2);
+}
+
+// Stores the terms of two cells: `aligned` (even column first) as one 32-bit word per term at
+// byte offset `off_lo`; otherwise the low cell at `off_lo` and the high cell at `off_hi` as
+// 16-bit halves.
+template <int NT, bool kRound>
+__device__ __forceinline__ void store_pair(unsigned char* term0, int off_lo, int off_hi,
+                                           bool aligned, float lo_cell, float hi_cell) {
+  uint32_t w[3];
+  split_pair<NT, kRound>(lo_cell, hi_cell, w);
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    unsigned char* base = term0 + t * kTermBytes;
+    if (aligned) {
+      *reinterpret_cast<uint32_t*>(base + off_lo) = w[t];
+    } else {
+      *reinterpret_cast<uint16_t*>(base + off_lo) = (uint16_t)(w[t] & 0xffffu);
+      *reinterpret_cast<uint16_t*>(base + off_hi) = (uint16_t)(w[t] >> 16);
+    }
+  }
+}
+
+// byte offset of window column c inside a term row (row part added by the caller)
+__device__ __forceinline__ int col_off(int c, int cg_bytes) {
+  return (c >> 3) * cg_bytes + (c & 7) * 2;
+}
+__device__ __forceinline__ int row_off(int r) { return (r >> 3) * kRowGroupBytes + (r & 7) * 16; }
+
+// Shared-memory plan (bytes from the start of dynamic shared memory).
+template <int NV, int NG, int kPrec>
+struct S2Smem {
+  static constexpr int kTerms = Terms<kPrec>::C + Terms<kPrec>::P;
+  static constexpr int kCg = col_group_bytes(kTerms);
+  static constexpr int kKzSlots = kS2Win / 16 + 2;              // circular k-steps of kz^T
+  static constexpr int kKzSlotBytes = kS2NK * 32;               // [NK][16] bf16
+  static constexpr int kQzBytes = kS2NK * kS2Rows * 2;
+  static constexpr int kGBytes = NV * kS2Rows * 2;
+  static constexpr int oTile = 0;
+  static constexpr int oQz = operand_bytes(kTerms);             // two buffers
+  static constexpr int oGhi = oQz + 2 * kQzBytes;               // two buffers
+  static constexpr int oGlo = oGhi + 2 * kGBytes;               // two buffers
+  static constexpr int oKz = oGlo + 2 * kGBytes;
+  static constexpr int oBar = oKz + kKzSlots * kKzSlotBytes;    // mbarrier, tmem pointer
+  static constexpr int oDq = oBar + 16;                         // row-sum terms of two warps
+  static constexpr int oS = oDq + 2 * kS2Rows * 16 * 4;         // [16][128] float2 evidence
+  static constexpr int oHam = oS + kS2Rows * kS2Threads * 8;    // [4][128] uint2 packed counts
+  static constexpr int oK = oHam + 4 * kS2Threads * 8;          // int tables from here
+  static constexpr int oKold = oK + kS2Win * 4;
+  static constexpr int oVb0 = oKold + kS2Win * 4;
+  static constexpr int oVb1 = oVb0 + kS2Win * 4;
+  static constexpr int oQ = oVb1 + kS2Win * 4;
+  static constexpr int oQold = oQ + kS2Rows * 4;
+  static constexpr int oKeep = oQold + kS2Rows * 4;             // [16][8] keep ballots
+  static constexpr int oRstat = oKeep + kS2Rows * kVjpWarps * 4;  // [16] float4
+  static constexpr int oGlut = oRstat + kS2Rows * 16;           // [64] float
+  static constexpr int oUlut = oGlut + 64 * 4;                  // [16][NG][16] float
+  static constexpr int kBytes = oUlut + kS2Rows * NG * 16 * 4;
+  static_assert(oQz % 16 == 0 && oS % 16 == 0 && oK % 16 == 0 && oRstat % 16 == 0, "alignment");
+};
+
+
+// ---- forward phase: four rows x two diagonals from the running state.  kw / kow hold the key
+// symbols (and the symbols leaving the horizon) of window columns cb .. cb + 5, cb the column of
+// (row r0, diagonal 1); cell (rr, e) reads entry rr + 1 - e.  Stores S per row and the eight
+// mismatch counts (times four: byte offsets into the gate table) as one 64-bit word.  Returns
+// whether any window product of the thread may be non-zero.
+template <bool kEdge>
+__device__ __forceinline__ bool s2_forward_group(const int* s_q, const int* s_qold,
+                                                 const float* glut, const int (&kw)[6],
+                                                 const int (&kow)[6], bool windowed, int r0, int i0,
+                                                 int j1, int W, int len, int hs_cut, float neg_md,
+                                                 float (&S)[2], int (&hs)[2], float2* s_row,
+                                                 uint2* ham_out) {
+  const int4 q4 = *reinterpret_cast<const int4*>(s_q + r0);
+  const int q[4] = {q4.x, q4.y, q4.z, q4.w};
+  int qo[4] = {0, 0, 0, 0};
+  if (windowed) {
+    const int4 o4 = *reinterpret_cast<const int4*>(s_qold + r0);
+    qo[0] = o4.x; qo[1] = o4.y; qo[2] = o4.z; qo[3] = o4.w;
+  }
+  int ham[4][2], hsv[4][2];
+  bool alive = false;
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int x = rr + 1 - e;
+      ham[rr][e] = __popc(q[rr] ^ kw[x]);
+      hsv[rr][e] = 0;
+      if (windowed) {
+        const int old = __popc(qo[rr] ^ kow[x]);
+        if (kEdge) {
+          const int j = j1 + x;
+          const bool act = j >= 0 && i0 + r0 + rr <= len - 1;
+          hs[e] += act ? ham[rr][e] - (j > W ? old : 0) : 0;
+          alive |= j >= W && hs[e] <= hs_cut;
+        } else {
+          hs[e] += ham[rr][e] - old;
+          alive |= hs[e] <= hs_cut;
+        }
+        hsv[rr][e] = hs[e];
+      }
+    }
+  float P[4][2];
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr) P[rr][0] = P[rr][1] = 0.0f;
+  const bool any_alive = windowed && __any_sync(0xffffffffu, alive);
+  if (any_alive) {
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        bool on = hsv[rr][e] <= hs_cut;
+        if (kEdge) on = on && (j1 + rr + 1 - e) >= W;
+        P[rr][e] = on ? __expf(neg_md * (float)hsv[rr][e]) : 0.0f;
+      }
+  }
+  uint32_t hw[2] = {0u, 0u};
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float x = glut[ham[rr][e]];
+      const float Sn = x * (1.0f + S[e]) - P[rr][e];
+      bool act = true;
+      if (kEdge) act = (j1 + rr + 1 - e) >= 0 && i0 + r0 + rr <= len - 1;
+      S[e] = act ? Sn : 0.0f;
+      hw[rr >> 1] |= (uint32_t)(ham[rr][e] * 4) << (8 * ((rr & 1) * 2 + e));
+    }
+    s_row[rr * kS2Threads] = make_float2(S[0], S[1]);
+  }
+  *ham_out = make_uint2(hw[0], hw[1]);
+  return any_alive;
+}
+
+// ---- adjoint phase, no window product alive: four rows (descending) x two diagonals.
+// sb is the running adjoint of S in float32 (a contraction here), xnext the gate one row
+// further down the diagonal.  Writes C and p*d into the operand area.
+template <int NG, int NC, int NP, bool kRound, bool kDropout, bool kEdge>
+__device__ __forceinline__ void s2_adjoint_group(
+    unsigned char* tC, unsigned char* tP, int cg, const float4* s_rstat, const uint32_t* s_keep,
+    const float* glut, const float* ulut, const uint32_t (&v0)[6], const uint32_t (&v1)[6],
+    const float2* s_row, uint2 hamw, int r0, int i0, int j1, int len, int skew, int cb, float mul2,
+    int keep_word, int keep_shift, float (&sb)[2], float (&xnext)[2]) {
+  // operand byte offsets of window columns cb .. cb + 4 (cb is even: cb + 1 and cb + 3 never
+  // start a new group of eight columns)
+  int o[5];
+  o[0] = col_off(cb, cg) + row_off(r0);
+  o[2] = col_off(cb + 2, cg) + row_off(r0);
+  o[4] = col_off(cb + 4, cg) + row_off(r0);
+  o[1] = o[0] + 2;
+  o[3] = o[2] + 2;
+#pragma unroll
+  for (int rr = 3; rr >= 0; --rr) {
+    const int r = r0 + rr;
+    const float4 st = s_rstat[r];          // (exponent bias, 1/Z, E * ds, 1/Z / keep probability)
+    const float2 Sv = s_row[rr * kS2Threads];
+    const uint32_t hb = rr < 2 ? hamw.x : hamw.y;
+    uint32_t kbits = 3u;
+    if (kDropout) kbits = s_keep[r * kVjpWarps + keep_word] >> keep_shift;
+    float Cv[2], pd[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int x = rr + 1 - e;
+      const float Se = e == 0 ? Sv.x : Sv.y;
+      const uint32_t hoff = (hb >> (8 * ((rr & 1) * 2 + e))) & 0xffu;
+      const float gate = *reinterpret_cast<const float*>(reinterpret_cast<const char*>(glut) + hoff);
+      const float t = 1.0f + Se;
+      const float rs = rsqrtf(t);
+      float ex = exp2f(fmaf(t * rs, mul2, st.x));
+      bool act = true;
+      if (kEdge) {
+        act = (j1 + x) >= 0 && i0 + r <= len - 1;
+        ex = act ? ex : 0.0f;
+      }
+      const float pr = ex * st.y;
+      pd[e] = ex * st.w;
+      if (kDropout) pd[e] = (kbits >> e & 1u) ? pd[e] : 0.0f;
+      else pd[e] = pr;
+      const float u = tiled_utility<NG>(ulut + r * NG * 16, v0[x], NG > 4 ? v1[x] : 0u);
+      const float dS = (pd[e] * u - pr * st.z) * rs;
+      sb[e] = fmaf(xnext[e], sb[e], dS);
+      Cv[e] = act ? Se * sb[e] : 0.0f;
+      xnext[e] = gate;
+    }
+    // diagonal 1 sits on the lower column (cb + rr), diagonal 0 on the next one
+    const bool aligned = (rr & 1) == 0;
+    store_pair<NC, kRound>(tC + rr * 16, o[rr], o[rr + 1], aligned, Cv[1], Cv[0]);
+    store_pair<NP, kRound>(tP + rr * 16, o[rr], o[rr + 1], aligned, pd[1], pd[0]);
+  }
+}
+
+struct S2Geom {
+  int w, rb, dmin, dmax, rb_lo, i0, first_row, skew, jwin;
+  int64_t ck_idx;
+};
+
+template <int NV, int NG, bool kDropout, int kPrec>
+__global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a) {
+  using L = S2Smem<NV, NG, kPrec>;
+  using TM = Terms<kPrec>;
+  constexpr int NC = TM::C, NP = TM::P, CG = L::kCg, NK = kS2NK;
+  extern __shared__ float4 smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(smem_raw);
+  unsigned char* tC = smem + L::oTile;                    // C terms, kTermBytes apart
+  unsigned char* tP = tC + NC * kTermBytes;             // p*d terms
+  unsigned char* bKz = smem + L::oKz;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + L::oBar);
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(mbar + 1);
+  float* s_dq = reinterpret_cast<float*>(smem + L::oDq);
+  float2* Sbuf = reinterpret_cast<float2*>(smem + L::oS);
+  uint2* Hbuf = reinterpret_cast<uint2*>(smem + L::oHam);
+  int* s_k = reinterpret_cast<int*>(smem + L::oK);
+  int* s_kold = reinterpret_cast<int*>(smem + L::oKold);
+  uint32_t* s_vb0 = reinterpret_cast<uint32_t*>(smem + L::oVb0);
+  uint32_t* s_vb1 = reinterpret_cast<uint32_t*>(smem + L::oVb1);
+  int* s_q = reinterpret_cast<int*>(smem + L::oQ);
+  int* s_qold = reinterpret_cast<int*>(smem + L::oQold);
+  uint32_t* s_keep = reinterpret_cast<uint32_t*>(smem + L::oKeep);
+  float4* s_rstat = reinterpret_cast<float4*>(smem + L::oRstat);
+  float* glut = reinterpret_cast<float*>(smem + L::oGlut);
+  float* ulut = reinterpret_cast<float*>(smem + L::oUlut);
+
+  Item it;
+  if (!load_item_1d(a, &it)) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool dense = a.plan.cu_seqlens == nullptr;
+  const int64_t sym_base = (int64_t)it.seq * a.sym_seq_stride + (int64_t)it.h * a.sym_head_stride +
+                           (dense ? 0 : it.start);
+  const int32_t* __restrict__ q = a.qsym + sym_base;
+  const int32_t* __restrict__ k = a.ksym + sym_base;
+  const int vh = it.h / a.group;
+  const uint32_t* __restrict__ vb = a.vbits + ((int64_t)vh * a.N + it.start) * a.vwords;
+  const int W = a.W, D = a.D, Dv = a.Dv, mask = a.mask, ring_slots = a.ring_slots;
+  const bool windowed = ring_slots > 0;
+  const float neg_md = -a.mismatch_scale / (float)a.D;
+  const int hs_cut = window_sum_cutoff(neg_md);
+  const float4* __restrict__ rowstat = a.rowstat + (int64_t)it.h * a.N + it.start;
+  float* ring = ring_slots ? a.ring + it.item_linear * (int64_t)ring_slots * kS2Band + kS2R * tid
+                           : nullptr;
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float mul2 = kSqrtScale * a.scale * kLog2e;
+  const float ds_mul = a.scale * (0.5f * kSqrtScale);   // folded into the utility tables and E
+  constexpr int NQ = 2;                                  // issuers of the row-sum k-loop
+  constexpr uint32_t kTmemCols = ((3 + NQ) * NK + 3 * NV) <= 128 ? 128 : 256;
+  constexpr uint32_t kColK = 0, kColV = 3 * NK, kColQ = 3 * NK + 3 * NV;
+
+  // ---- one-time set-up
+  for (int e = tid; e < operand_bytes(L::kTerms) / 16; e += kS2Threads)
+    reinterpret_cast<uint4*>(tC)[e] = make_uint4(0, 0, 0, 0);
+  if (tid <= D) glut[tid] = expf(neg_md * (float)tid);
+  if (warp == 0) tc::tmem_alloc(tmem_ptr, kTmemCols);
+  if (tid == 0) tc::mbar_init(mbar, 4);
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  tc::fence_after_thread_sync();
+  const uint32_t tmem = *tmem_ptr;
+  uint32_t mma_phase = 0;
+  bool mma_timed_out = false;
+  int buf = 0;
+
+  auto geom_of = [&](int w, int rb) {
+    S2Geom g;
+    g.w = w;
+    g.rb = rb;
+    g.dmin = 1 + w * kS2Band;
+    g.dmax = g.dmin + kS2Band - 1;
+    g.rb_lo = g.dmin / kS2Rows;
+    g.i0 = rb * kS2Rows;
+    g.first_row = max(g.i0, g.dmin);
+    g.skew = g.first_row - g.i0;
+    g.jwin = g.i0 - g.dmax;
+    g.ck_idx = it.ck_base + vjp_ck_before(it.len, w) + (rb - g.rb_lo);
+    return g;
+  };
+
+  // Adds the accumulators of a finished block to the per-item partial gradient rows.  Warp q
+  // owns tensor-memory lanes 32 q .. 32 q + 31, i.e. window columns chunk + 32 q + lane of the
+  // column sums and one 16-row term slice of the row sums.
+  auto epilogue = [&](int block_w, int block_rb) {
+    const S2Geom b = geom_of(block_w, block_rb);
+    if (!mma_timed_out && !__all_sync(0xffffffffu, tc::mbar_wait(mbar, mma_phase, 1u << 24)))
+      mma_timed_out = true;
+    if (mma_timed_out) {   // nothing accumulated may be trusted; keep the named barrier whole
+      if ((mask & 1) && warp < NC) asm volatile("bar.sync 1, %0;" ::"n"(32 * NC) : "memory");
+      return;
+    }
+    mma_phase ^= 1u;
+    tc::fence_after_thread_sync();
+    const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
+#pragma unroll
+    for (int ch = 0; ch < 3; ++ch) {
+      // only window columns >= 256 of the last chunk are new: they sit in the last quarter
+      if (ch == 2 && warp < 3) continue;
+      const int c = chunk_start(ch) + 32 * warp + lane;
+      const int j = b.jwin + c;
+      const bool use = (ch < 2 || c >= 256) && j >= 0 && j <= it.len - 1 - b.dmin;
+      const int i_top = min(j + b.dmax, it.len - 1);
+      const bool first = (b.w == it.w_begin) && (b.rb == i_top / kS2Rows);
+      if (mask & 2) {
+        float v[16];
+        tc::tmem_ld16(tmem + lane_base + kColK + ch * NK, v);
+        if (use) {
+          float* dst = a.dk_part + (it.rowslot + j) * D;
+          if ((D & 3) == 0) {
+#pragma unroll
+            for (int d4 = 0; d4 < 4; ++d4)
+              if (4 * d4 < D) {
+                float4* p4 = reinterpret_cast<float4*>(dst) + d4;
+                float4 o = first ? make_float4(0.f, 0.f, 0.f, 0.f) : *p4;
+                o.x += v[4 * d4]; o.y += v[4 * d4 + 1]; o.z += v[4 * d4 + 2]; o.w += v[4 * d4 + 3];
+                *p4 = o;
+              }
+          } else {
+#pragma unroll
+            for (int d = 0; d < 16; ++d)
+              if (d < D) dst[d] = first ? v[d] : dst[d] + v[d];
+          }
+        }
+      }
+      if (mask & 4) {
+#pragma unroll
+        for (int n0 = 0; n0 < NV; n0 += 16) {
+          float v[16];
+          tc::tmem_ld16(tmem + lane_base + kColV + ch * NV + n0, v);
+          if (use && n0 < Dv) {
+            float* dst = a.dv_part + (it.rowslot + j + 1) * Dv + n0;
+            if ((Dv & 3) == 0) {
+#pragma unroll
+              for (int d4 = 0; d4 < 4; ++d4)
+                if (n0 + 4 * d4 < Dv) {
+                  float4* p4 = reinterpret_cast<float4*>(dst) + d4;
+                  float4 o = first ? make_float4(0.f, 0.f, 0.f, 0.f) : *p4;
+                  o.x += v[4 * d4]; o.y += v[4 * d4 + 1]; o.z += v[4 * d4 + 2]; o.w += v[4 * d4 + 3];
+                  *p4 = o;
+                }
+            } else {
+#pragma unroll
+              for (int d = 0; d < 16; ++d)
+                if (n0 + d < Dv) dst[d] = first ? v[d] : dst[d] + v[d];
+            }
+          }
+        }
+      }
+    }
+    if ((mask & 1) && warp < NC) {
+      // accumulator rows 16 t .. 16 t + 15 (term t of C) sit in lanes 0-15 of lane quarter t
+      float v[16], v2[16];
+      tc::tmem_ld16(tmem + lane_base + kColQ, v);
+      tc::tmem_ld16(tmem + lane_base + kColQ + NK, v2);
+#pragma unroll
+      for (int d = 0; d < 16; ++d) v[d] += v2[d];
+      if (warp > 0 && lane < kS2Rows) {
+        float4* dst4 = reinterpret_cast<float4*>(s_dq + ((warp - 1) * kS2Rows + lane) * 16);
+#pragma unroll
+        for (int d4 = 0; d4 < 4; ++d4)
+          dst4[d4] = make_float4(v[4 * d4], v[4 * d4 + 1], v[4 * d4 + 2], v[4 * d4 + 3]);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * NC) : "memory");
+      const int i = b.i0 + lane;
+      if (warp == 0 && lane < kS2Rows && i >= b.first_row && i <= it.len - 1) {
+        float* dst = a.dq_part + (it.rowslot + i) * D;
+#pragma unroll
+        for (int d = 0; d < 16; ++d) {
+          float sum = v[d];
+#pragma unroll
+          for (int t = 1; t < NC; ++t) sum += s_dq[((t - 1) * kS2Rows + lane) * 16 + d];
+          if (d < D) dst[d] = (b.w == it.w_begin) ? sum : dst[d] + sum;
+        }
+      }
+    }
+    tc::fence_before_thread_sync();
+  };
+
+  const int rb_top = (it.len - 1) / kS2Rows;     // bottom row block of every band
+  const float inv_keep = a.inv_keep;
+  const int keep_word = tid >> 4, keep_shift = 2 * (tid & 15);
+
+  // Tables of one block: column windows, row symbols and statistics, keep ballots, utility
+  // tables (scaled by ds_mul: the adjoint seed then needs no further factor) and the
+  // grad_output operand of the value sums.
+  auto fill_tables = [&](const S2Geom& g, unsigned char* bGhi, unsigned char* bGlo) {
+    for (int c = tid; c < kS2Win; c += kS2Threads) {
+      const int j = g.jwin + c;
+      const bool in = j >= 0 && j < it.len - 1;
+      s_k[c] = in ? __ldg(k + j) : 0;
+      const int jo = j - W - 1;
+      s_kold[c] = (windowed && jo >= 0 && jo < it.len) ? __ldg(k + jo) : 0;
+      const uint32_t bits = in ? __ldg(vb + j + 1) : 0u;
+      s_vb0[c] = spread_nibbles(bits & 0xffffu);
+      if (NG > 4) s_vb1[c] = spread_nibbles(bits >> 16);
+    }
+    if (tid < kS2Rows) {
+      const int i = g.i0 + tid;
+      const bool in = i >= g.first_row && i <= it.len - 1;
+      s_q[tid] = in ? __ldg(q + i) : 0;
+      s_qold[tid] = (windowed && in && i - W - 1 >= 0) ? __ldg(q + i - W - 1) : 0;
+      float4 st = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (in) st = rowstat[i];                       // (max, 1/Z, E, log i)
+      s_rstat[tid] = make_float4(-(st.w + st.x) * kLog2e - mul2, st.y, st.z * ds_mul,
+                                 st.y * inv_keep);
+    }
+    if (kDropout) {
+      const int r = tid >> 3, ro = r - g.skew;
+      s_keep[tid] = (ro >= 0 && g.i0 + r <= it.len - 1)
+                        ? a.keepbits[(g.ck_idx * kS2Rows + ro) * kVjpWarps + (tid & 7)]
+                        : 0u;
+    }
+    for (int e = tid; e < kS2Rows * NG; e += kS2Threads) {
+      const int r = e / NG, gq = e - r * NG;
+      const int i = g.i0 + r;
+      float gv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      if (i >= g.first_row && i <= it.len - 1) {
+        const int64_t base = (((int64_t)it.start + i) * a.H + it.h) * Dv + 4 * gq;
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if (4 * gq + b < Dv) gv[b] = ds_mul * load_as_float(a.go, base + b, a.dtype);
+      }
+      float4* dst = reinterpret_cast<float4*>(ulut + e * 16);
+#pragma unroll
+      for (int n4 = 0; n4 < 4; ++n4) {
+        const float hi = ((n4 & 1) ? gv[2] : -gv[2]) + ((n4 & 2) ? gv[3] : -gv[3]);
+        dst[n4] = make_float4(hi - gv[0] - gv[1], hi + gv[0] - gv[1], hi - gv[0] + gv[1],
+                              hi + gv[0] + gv[1]);
+      }
+    }
+    if (mask & 4)
+      for (int e = tid; e < NV * kS2Rows; e += kS2Threads) {
+        const int d = e / kS2Rows, r = e - d * kS2Rows;
+        const int i = g.i0 + r;
+        float v = 0.0f;
+        if (d < Dv && i >= g.first_row && i <= it.len - 1)
+          v = load_as_float(a.go, (((int64_t)it.start + i) * a.H + it.h) * Dv + d, a.dtype);
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        *reinterpret_cast<__nv_bfloat16*>(bGhi + b_off(d, r, NV)) = h;
+        if (TM::glo)
+          *reinterpret_cast<__nv_bfloat16*>(bGlo + b_off(d, r, NV)) =
+              __float2bfloat16_rn(v - __bfloat162float(h));
+      }
+  };
+
+  int w = it.w_begin, rb = rb_top;
+  int prev_w = 0, prev_rb = 0;
+  bool prev_pending = false, band_start = true;
+  // per-band state of the thread's two diagonals
+  float sb[2] = {0.f, 0.f}, xnext[2] = {0.f, 0.f};
+  double Sbar[2] = {0.0, 0.0}, Y[2] = {0.0, 0.0};
+  int live = 0;
+  bool ring_dirty = false;
+
+  while (true) {
+    const S2Geom g = geom_of(w, rb);
+    const int delta0 = g.dmin + kS2R * tid;            // diagonal of e = 0
+    if (band_start) {
+      sb[0] = sb[1] = xnext[0] = xnext[1] = 0.0f;
+      Sbar[0] = Sbar[1] = Y[0] = Y[1] = 0.0;
+      live = 0;
+      ring_dirty = false;
+      // the bottom block of a band refills the whole kz^T ring: the last block of the previous
+      // band must have released it
+      if (prev_pending) {
+        epilogue(prev_w, prev_rb);
+        prev_pending = false;
+      }
+    }
+    const bool next_same = rb > g.rb_lo;
+    const bool has_next = next_same || w + 1 < it.w_end;
+    unsigned char* bQz = smem + L::oQz + buf * L::kQzBytes;
+    unsigned char* bGhi = smem + L::oGhi + buf * L::kGBytes;
+    unsigned char* bGlo = smem + L::oGlo + buf * L::kGBytes;
+
+    fill_tables(g, bGhi, bGlo);
+    const int4 ck = *reinterpret_cast<const int4*>(a.ckpt + g.ck_idx * kS2Band + kS2R * tid);
+    __syncthreads();                                   // sync 1: tables complete
+
+    // ---- B operands that come from the tables
+    if (mask & 2)
+      for (int e = tid; e < NK * kS2Rows; e += kS2Threads) {
+        const int d = e / kS2Rows, r = e - d * kS2Rows;
+        const int i = g.i0 + r;
+        const float v = (d < D && i >= g.first_row && i <= it.len - 1)
+                            ? ((s_q[r] >> d & 1) ? 1.0f : -1.0f) : 0.0f;
+        *reinterpret_cast<__nv_bfloat16*>(bQz + b_off(d, r, NK)) = __float2bfloat16_rn(v);
+      }
+    if (mask & 1) {
+      const int g0 = (g.jwin + (1 << 20)) >> 4;        // absolute group of window column 0
+      const int nfill = band_start ? kS2Win / 16 : 1;
+      for (int e = tid; e < nfill * NK * 16; e += kS2Threads) {
+        const int ks = e / (NK * 16), rem = e - ks * (NK * 16);
+        const int d = rem >> 4, cc = rem & 15;
+        const int c = ks * 16 + cc;
+        const int j = g.jwin + c;
+        const float v = (d < D && j >= 0 && j < it.len - 1)
+                            ? ((s_k[c] >> d & 1) ? 1.0f : -1.0f) : 0.0f;
+        const int sl = (g0 + ks) % L::kKzSlots;
+        *reinterpret_cast<__nv_bfloat16*>(bKz + sl * L::kKzSlotBytes + b_off(d, cc, NK)) =
+            __float2bfloat16_rn(v);
+      }
+    }
+
+    // ---- phase A: forward recurrence of the block from its checkpoint
+    float S[2] = {__int_as_float(ck.x), __int_as_float(ck.z)};
+    int hs[2] = {ck.y, ck.w};
+    const bool interior = g.jwin >= (windowed ? W + 1 : 0) && g.i0 + kS2Rows - 1 <= it.len - 1;
+    const int cb0 = kS2Band - 2 - kS2R * tid;          // window column of (row 0, diagonal 1)
+    bool has_p = false;
+    {
+      int kw[6], kow[6] = {0, 0, 0, 0, 0, 0};
+      const int2 a0 = *reinterpret_cast<const int2*>(s_k + cb0);
+      kw[0] = a0.x; kw[1] = a0.y;
+      if (windowed) {
+        const int2 b0 = *reinterpret_cast<const int2*>(s_kold + cb0);
+        kow[0] = b0.x; kow[1] = b0.y;
+      }
+#pragma unroll 1
+      for (int r0 = 0; r0 < kS2Rows; r0 += 4) {
+        const int cb = cb0 + r0;
+        const int2 a1 = *reinterpret_cast<const int2*>(s_k + cb + 2);
+        const int2 a2 = *reinterpret_cast<const int2*>(s_k + cb + 4);
+        kw[2] = a1.x; kw[3] = a1.y; kw[4] = a2.x; kw[5] = a2.y;
+        if (windowed) {
+          const int2 b1 = *reinterpret_cast<const int2*>(s_kold + cb + 2);
+          const int2 b2 = *reinterpret_cast<const int2*>(s_kold + cb + 4);
+          kow[2] = b1.x; kow[3] = b1.y; kow[4] = b2.x; kow[5] = b2.y;
+        }
+        const int j1 = g.jwin + cb;                    // key column of (row r0, diagonal 1)
+        float2* s_row = Sbuf + r0 * kS2Threads + tid;
+        uint2* ham_out = Hbuf + (r0 >> 2) * kS2Threads + tid;
+        if (interior)
+          has_p |= s2_forward_group<false>(s_q, s_qold, glut, kw, kow, windowed, r0, g.i0, j1, W,
+                                           it.len, hs_cut, neg_md, S, hs, s_row, ham_out);
+        else
+          has_p |= s2_forward_group<true>(s_q, s_qold, glut, kw, kow, windowed, r0, g.i0, j1, W,
+                                          it.len, hs_cut, neg_md, S, hs, s_row, ham_out);
+        kw[0] = kw[4]; kw[1] = kw[5];
+        kow[0] = kow[4]; kow[1] = kow[5];
+      }
+    }
+
+    // ---- the previous block's MMAs have had the whole table / forward phase to finish
+    if (prev_pending) epilogue(prev_w, prev_rb);
+
+    // ---- phase B: adjoint recurrence, rows descending; C and p*d go to the operand area
+    const bool warp_p = windowed && ring != nullptr && has_p;
+    if (!warp_p && live == 0) {
+      sb[0] = (float)Sbar[0];
+      sb[1] = (float)Sbar[1];
+      uint32_t v0[6], v1[6] = {0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll 1
+      for (int r0 = kS2Rows - 4; r0 >= 0; r0 -= 4) {
+        const int cb = cb0 + r0;
+#pragma unroll
+        for (int x2 = 0; x2 < 3; ++x2) {
+          const uint2 t0 = *reinterpret_cast<const uint2*>(s_vb0 + cb + 2 * x2);
+          v0[2 * x2] = t0.x; v0[2 * x2 + 1] = t0.y;
+          if (NG > 4) {
+            const uint2 t1 = *reinterpret_cast<const uint2*>(s_vb1 + cb + 2 * x2);
+            v1[2 * x2] = t1.x; v1[2 * x2 + 1] = t1.y;
+          }
+        }
+        const float2* s_row = Sbuf + r0 * kS2Threads + tid;
+        const uint2 hamw = Hbuf[(r0 >> 2) * kS2Threads + tid];
+        const int j1 = g.jwin + cb;
+        if (interior)
+          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, false>(tC, tP, CG, s_rstat, s_keep, glut, ulut, v0,
+                                                        v1, s_row, hamw, r0, g.i0, j1, it.len,
+                                                        g.skew, cb, mul2, keep_word, keep_shift,
+                                                        sb, xnext);
+        else
+          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, true>(tC, tP, CG, s_rstat, s_keep, glut, ulut, v0,
+                                                       v1, s_row, hamw, r0, g.i0, j1, it.len,
+                                                       g.skew, cb, mul2, keep_word, keep_shift, sb,
+                                                       xnext);
+      }
+      Sbar[0] = (double)sb[0];
+      Sbar[1] = (double)sb[1];
+    } else {
+      // A window product is (or recently was) alive in this warp.  The product is rebuilt from
+      // the mismatch-count sum walked backwards (hs ended phase A on the block's last row); the
+      // sliding sum Y of Sbar * P over W + 1 rows lives in a ring indexed by the row, so a warp
+      // reads and writes one contiguous line per row.
+#pragma unroll 1
+      for (int r = kS2Rows - 1; r >= 0; --r) {
+        const int i = g.i0 + r;
+        const float4 st = s_rstat[r];
+        const float2 Sv2 = Sbuf[r * kS2Threads + tid];
+        const uint2 hamw = Hbuf[(r >> 2) * kS2Threads + tid];
+        const uint32_t hb = (r & 3) < 2 ? hamw.x : hamw.y;
+        uint32_t kbits = 3u;
+        if (kDropout) kbits = s_keep[r * kVjpWarps + keep_word] >> keep_shift;
+        const int qo = s_qold[r];
+        float Cv[2], pd[2], Pv[2], gate[2], dS[2];
+        bool act[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int c = r + kS2Band - 1 - kS2R * tid - e;
+          const int j = g.jwin + c;
+          act[e] = j >= 0 && i <= it.len - 1;
+          const uint32_t hoff = (hb >> (8 * ((r & 1) * 2 + e))) & 0xffu;
+          const int ham = (int)(hoff >> 2);
+          gate[e] = glut[ham];
+          Pv[e] = (act[e] && j >= W) ? __expf(neg_md * (float)hs[e]) : 0.0f;
+          hs[e] += ((act[e] && j > W) ? __popc(qo ^ s_kold[c]) : 0) - (act[e] ? ham : 0);
+          const float Se = e == 0 ? Sv2.x : Sv2.y;
+          const float t = 1.0f + Se;
+          const float rs = rsqrtf(t);
+          const float ex = act[e] ? exp2f(fmaf(t * rs, mul2, st.x)) : 0.0f;
+          const float pr = ex * st.y;
+          pd[e] = ex * st.w;
+          if (kDropout) pd[e] = (kbits >> e & 1u) ? pd[e] : 0.0f;
+          const float u = tiled_utility<NG>(ulut + r * NG * 16, s_vb0[c], NG > 4 ? s_vb1[c] : 0u);
+          dS[e] = (pd[e] * u - pr * st.z) * rs;
+          if (act[e]) Sbar[e] = (double)dS[e] + (double)xnext[e] * Sbar[e];
+        }
+        const bool any_p = __any_sync(0xffffffffu, Pv[0] != 0.0f || Pv[1] != 0.0f);
+        if (any_p) {
+          live = W + 2;
+          ring_dirty = true;
+        }
+        if (live > 0) {
+          float* line = ring + (int64_t)(i % ring_slots) * kS2Band;
+#pragma unroll
+          for (int e = 0; e < 2; ++e)
+            if (act[e]) {
+              const float tf = (float)(Sbar[e] * (double)Pv[e]);
+              const float old = line[e];
+              line[e] = tf;
+              Y[e] += (double)tf - (double)old;
+            }
+          if (--live == 0) Y[0] = Y[1] = 0.0;
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float Se = e == 0 ? Sv2.x : Sv2.y;
+          Cv[e] = act[e] ? (float)((double)(Se + Pv[e]) * Sbar[e] - Y[e]) : 0.0f;
+          if (act[e]) xnext[e] = gate[e];
+        }
+        const int c1 = r + kS2Band - 2 - kS2R * tid;           // column of diagonal 1
+        const int off_lo = col_off(c1, CG) + row_off(r), off_hi = col_off(c1 + 1, CG) + row_off(r);
+        if ((r & 1) == 0) {
+          store_pair<NC, kPrec == 0>(tC, off_lo, off_hi, true, Cv[1], Cv[0]);
+          store_pair<NP, kPrec == 0>(tP, off_lo, off_hi, true, pd[1], pd[0]);
+        } else {
+          store_pair<NC, kPrec == 0>(tC, off_lo, off_hi, false, Cv[1], Cv[0]);
+          store_pair<NP, kPrec == 0>(tP, off_lo, off_hi, false, pd[1], pd[0]);
+        }
+      }
+    }
+    (void)delta0;
+
+    // ---- phase C: hand the operands to the tensor core
+    tc::fence_proxy_async_smem();
+    tc::fence_before_thread_sync();
+    __syncthreads();                               // sync 2: tiles and B operands complete
+    if (lane == 0 && !mma_timed_out) {
+      tc::fence_after_thread_sync();
+      constexpr uint32_t idK = tc::idesc_bf16_f32(128, NK, true, false);
+      constexpr uint32_t idV = tc::idesc_bf16_f32(128, NV, true, false);
+      constexpr uint32_t idQ = tc::idesc_bf16_f32(64, NK, false, false);
+      if (warp == 0 && (mask & 2)) {
+        const uint64_t dQz = tc::smem_desc(tc::smem_addr(bQz), NK / 8 * 128, 128);
+        const uint64_t c0 = tc::smem_desc(tc::smem_addr(tC), kRowGroupBytes, CG);
+        const uint64_t c1 = tc::smem_desc(tc::smem_addr(tC + kTermBytes), kRowGroupBytes, CG);
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) {
+          const uint64_t shift = (uint64_t)(((chunk_start(ch) >> 3) * CG) >> 4);
+          tc::mma_bf16(tmem + kColK + ch * NK, c0 + shift, dQz, idK, false);
+          tc::mma_bf16(tmem + kColK + ch * NK, c1 + shift, dQz, idK, true);
+        }
+      }
+      if (warp == 1 && (mask & 4)) {
+        const uint64_t dGhi = tc::smem_desc(tc::smem_addr(bGhi), NV / 8 * 128, 128);
+        const uint64_t dGlo = tc::smem_desc(tc::smem_addr(bGlo), NV / 8 * 128, 128);
+        const uint64_t p0 = tc::smem_desc(tc::smem_addr(tP), kRowGroupBytes, CG);
+        const uint64_t p1 = tc::smem_desc(tc::smem_addr(tP + kTermBytes), kRowGroupBytes, CG);
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) {
+          const uint64_t shift = (uint64_t)(((chunk_start(ch) >> 3) * CG) >> 4);
+          tc::mma_bf16(tmem + kColV + ch * NV, p0 + shift, dGhi, idV, false);
+          if (NP == 2) tc::mma_bf16(tmem + kColV + ch * NV, p1 + shift, dGhi, idV, true);
+          if (TM::glo) tc::mma_bf16(tmem + kColV + ch * NV, p0 + shift, dGlo, idV, true);
+        }
+      }
+      if (warp >= 2 && (mask & 1)) {
+        // K-major view (row sums): K direction = column groups, M direction = the row groups of
+        // the C terms of a column group (M = 64: the rows past the last term alias p*d cores)
+        const uint64_t kC = tc::smem_desc(tc::smem_addr(tC), CG, kRowGroupBytes);
+        const uint64_t dKz0 = tc::smem_desc(tc::smem_addr(bKz), NK / 8 * 128, 128);
+        constexpr int kSteps = kS2Win / 16;
+        const int part = warp - 2;
+        const int ks0 = part * kSteps / NQ, ks1 = (part + 1) * kSteps / NQ;
+        const uint32_t acc = tmem + kColQ + part * NK;
+        const int g0 = (g.jwin + (1 << 20)) >> 4;
+        int sl = (g0 + ks0) % L::kKzSlots;
+#pragma unroll 1
+        for (int ks = ks0; ks < ks1; ++ks) {
+          const uint64_t dKz = dKz0 + (uint64_t)((sl * L::kKzSlotBytes) >> 4);
+          const uint64_t shift = (uint64_t)((ks * 2 * CG) >> 4);
+          tc::mma_bf16(acc, kC + shift, dKz, idQ, ks > ks0);
+          sl = sl + 1 == L::kKzSlots ? 0 : sl + 1;
+        }
+      }
+      tc::mma_commit(mbar);
+    }
+    prev_w = w;
+    prev_rb = rb;
+    prev_pending = true;
+    buf ^= 1;
+    // leave the ring zeroed for the next band of this item
+    if (!next_same && ring != nullptr && ring_dirty && has_next)
+      for (int sl = 0; sl < ring_slots; ++sl) {
+        ring[(int64_t)sl * kS2Band] = 0.0f;
+        ring[(int64_t)sl * kS2Band + 1] = 0.0f;
+      }
+    if (!has_next) break;
+    band_start = !next_same;
+    if (next_same) {
+      --rb;
+    } else {
+      ++w;
+      rb = rb_top;
+    }
+  }
+  if (prev_pending) epilogue(prev_w, prev_rb);
+  __syncthreads();
+  if (mma_timed_out && lane == 0) atomicExch(a.plan.status + 1, 1);
+  if (warp == 0) tc::tmem_dealloc(tmem, kTmemCols);
+}
+
+template <int NV, int NG, bool kDropout, int kPrec>
+int launch_s2_tiled_t(const VjpArgs& a, unsigned grid, cudaStream_t stream) {
+  constexpr int bytes = S2Smem<NV, NG, kPrec>::kBytes;
+  auto kernel = vjp_sweep2_tiled_kernel<NV, NG, kDropout, kPrec>;
+  ROSA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  kernel<<<grid, kS2Threads, bytes, stream>>>(a);
+  ROSA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+template <int NV, int NG>
+int launch_s2_tiled_n(const VjpArgs& a, unsigned grid, cudaStream_t stream) {
+  const bool dropout = a.dropout_p > 0.0f;
+  const int prec = a.dtype == ROSA_B200_F32 ? 0 : a.dtype == ROSA_B200_F16 ? 1 : 2;
+#define ROSA_S2(DO, PR) launch_s2_tiled_t<NV, NG, DO, PR>(a, grid, stream)
+  if (dropout) return prec == 0 ? ROSA_S2(true, 0) : prec == 1 ? ROSA_S2(true, 1) : ROSA_S2(true, 2);
+  return prec == 0 ? ROSA_S2(false, 0) : prec == 1 ? ROSA_S2(false, 1) : ROSA_S2(false, 2);
+#undef ROSA_S2
+}
+
+}  // namespace
+
+int launch_vjp_sweep2_tiled(const VjpArgs& a, int items_upper, cudaStream_t stream) {
+  const unsigned grid = (unsigned)((int64_t)items_upper * a.H);
+  if (a.Dv <= 8) return launch_s2_tiled_n<16, 2>(a, grid, stream);
+  if (a.Dv <= 16) return launch_s2_tiled_n<16, 4>(a, grid, stream);
+  return launch_s2_tiled_n<32, 8>(a, grid, stream);
+}
+
+}  // namespace rosa

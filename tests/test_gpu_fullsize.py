@@ -11,7 +11,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-from tests.helpers import nonzero_randn, normalised_error, repeated_stream_logits
+from tests.helpers import grad_tol, nonzero_randn, normalised_error, repeated_stream_logits
 
 DEV = "cuda"
 GRAD_TOL = 1e-4
@@ -51,9 +51,9 @@ def test_training_shape_sampled_slices_against_oracle(cabi, dtype):
         rq, rk, rv = orc.surrogate_vjp(f(q[rows, hs]), f(k[rows, hs]), f(v[rows, vh:vh + 1]),
                                        f(go[rows, hs]), cu, W, 1.0, p, m, seed, batch_offset=b,
                                        head_offset=vh * group)
-        assert normalised_error(f(dq[rows, hs]), rq) <= GRAD_TOL
-        assert normalised_error(f(dk[rows, hs]), rk) <= GRAD_TOL
-        assert normalised_error(f(dv[rows, vh:vh + 1]), rv) <= GRAD_TOL
+        assert normalised_error(f(dq[rows, hs]), rq) <= grad_tol(dtype)
+        assert normalised_error(f(dk[rows, hs]), rk) <= grad_tol(dtype)
+        assert normalised_error(f(dv[rows, vh:vh + 1]), rv) <= grad_tol(dtype)
 
 
 def test_long_match_stress_full_length_properties(cabi):
@@ -80,12 +80,12 @@ def test_long_match_stress_full_length_properties(cabi):
     # stress case cancel and amplify the rounding noise to a few 1e-5 of the largest entry)
     for a, b, c in ((dq1, dq2, dqs), (dk1, dk2, dks), (dv1, dv2, dvs)):
         err = normalised_error((a + b).cpu().numpy(), c.cpu().numpy())
-        assert err <= GRAD_TOL, err
+        assert err <= grad_tol(torch.bfloat16), err   # bf16-input runs against a float32-input run
     # tensor-core and CUDA-core contractions of the same tiles agree
     cc = _vjp(cabi, q, k, v, g1, (1, T), W, 1.0, 0.0, 3.0, 0, mask=7 | 0x100)[2:]
     for a, b in zip((dq1, dk1, dv1), cc):
         err = normalised_error(a.cpu().numpy(), b.cpu().numpy())
-        assert err <= 5e-5, err
+        assert err <= grad_tol(torch.bfloat16), err
     # the last key position of the sequence receives no gradient
     assert torch.all(dk1[T - 1] == 0) and torch.all(dv1[0] == 0)
 

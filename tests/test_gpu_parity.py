@@ -12,7 +12,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-from tests.helpers import (TORCH_DTYPES, nonzero_randn, normalised_error, oracle_forward,
+from tests.helpers import (TORCH_DTYPES, grad_tol, nonzero_randn, normalised_error, oracle_forward,
                            oracle_grads, repeated_stream_logits)
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
@@ -118,7 +118,7 @@ def test_random_dense_against_oracle(cabi, shape):
     assert np.array_equal(routes.cpu().numpy(), want)
     rq, rk, rv = oracle_grads(q, k, v, go, cu, W, scale, p, m, 77)
     for mine, ref in ((dq, rq), (dk, rk), (dv, rv)):
-        assert normalised_error(mine.cpu().numpy(), ref) <= GRAD_TOL
+        assert normalised_error(mine.cpu().numpy(), ref) <= grad_tol(dt)
 
 
 @pytest.mark.parametrize("bits,W,T", [(2, 16, 600), (1, 8, 300), (2, 300, 520)])
@@ -185,7 +185,7 @@ def test_tensor_core_and_cuda_core_contractions_agree(cabi):
         tc = _run_cabi(cabi, q, k, v, go, (1, T), W, 1.0, p, 3.0, 5)[4:]
         cc = _run_cabi(cabi, q, k, v, go, (1, T), W, 1.0, p, 3.0, 5, mask=7 | 0x100)[4:]
         for x, y in zip(tc, cc):
-            assert normalised_error(x.cpu().numpy(), y.cpu().numpy()) <= 2e-5
+            assert normalised_error(x.cpu().numpy(), y.cpu().numpy()) <= max(2e-5, grad_tol(dt) / 2)
 
 
 def test_backward_is_bitwise_reproducible(cabi):
