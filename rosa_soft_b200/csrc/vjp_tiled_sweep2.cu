@@ -392,6 +392,34 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
   // column sums and one 16-row term slice of the row sums.
   auto epilogue = [&](int block_w, int block_rb) {
     const S2Geom b = geom_of(block_w, block_rb);
+    const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
+    // Rows of at most 8 components (the common shapes): the partial rows that the accumulators
+    // are added to are requested BEFORE the wait for the tensor core, so the round trip to L2
+    // overlaps the wait instead of following it.
+    const bool small = NG == 2 && D <= 8 && (D & 3) == 0 && (Dv & 3) == 0;
+    float4 prior_k[3][2], prior_v[3][2];
+    float* dst_k[3];
+    float* dst_v[3];
+    bool use3[3];
+#pragma unroll
+    for (int ch = 0; ch < 3; ++ch) {
+      const int c = chunk_start(ch) + 32 * warp + lane;
+      const int j = b.jwin + c;
+      // only window columns >= 256 of the last chunk are new: they sit in the last quarter
+      use3[ch] = (ch < 2 || (warp == 3 && c >= 256)) && j >= 0 && j <= it.len - 1 - b.dmin;
+      const int i_top = min(j + b.dmax, it.len - 1);
+      const bool first = (b.w == it.w_begin) && (b.rb == i_top / kS2Rows);
+      dst_k[ch] = a.dk_part + (it.rowslot + j) * D;
+      dst_v[ch] = a.dv_part + (it.rowslot + j + 1) * Dv;
+#pragma unroll
+      for (int d4 = 0; d4 < 2; ++d4) {
+        prior_k[ch][d4] = prior_v[ch][d4] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (small && use3[ch] && !first) {
+          if ((mask & 2) && 4 * d4 < D) prior_k[ch][d4] = reinterpret_cast<const float4*>(dst_k[ch])[d4];
+          if ((mask & 4) && 4 * d4 < Dv) prior_v[ch][d4] = reinterpret_cast<const float4*>(dst_v[ch])[d4];
+        }
+      }
+    }
     if (!mma_timed_out && !__all_sync(0xffffffffu, tc::mbar_wait(mbar, mma_phase, 1u << 24)))
       mma_timed_out = true;
     if (mma_timed_out) {   // nothing accumulated may be trusted; keep the named barrier whole
@@ -400,21 +428,51 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
     }
     mma_phase ^= 1u;
     tc::fence_after_thread_sync();
-    const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
+    if (small) {
+#pragma unroll
+      for (int ch = 0; ch < 3; ++ch) {
+        if (ch == 2 && warp < 3) continue;
+        if (mask & 2) {
+          float v[16];
+          tc::tmem_ld16(tmem + lane_base + kColK + ch * NK, v);
+          if (use3[ch]) {
+#pragma unroll
+            for (int d4 = 0; d4 < 2; ++d4)
+              if (4 * d4 < D) {
+                float4 o = prior_k[ch][d4];
+                o.x += v[4 * d4]; o.y += v[4 * d4 + 1]; o.z += v[4 * d4 + 2]; o.w += v[4 * d4 + 3];
+                reinterpret_cast<float4*>(dst_k[ch])[d4] = o;
+              }
+          }
+        }
+        if (mask & 4) {
+          float v[16];
+          tc::tmem_ld16(tmem + lane_base + kColV + ch * NV, v);
+          if (use3[ch]) {
+#pragma unroll
+            for (int d4 = 0; d4 < 2; ++d4)
+              if (4 * d4 < Dv) {
+                float4 o = prior_v[ch][d4];
+                o.x += v[4 * d4]; o.y += v[4 * d4 + 1]; o.z += v[4 * d4 + 2]; o.w += v[4 * d4 + 3];
+                reinterpret_cast<float4*>(dst_v[ch])[d4] = o;
+              }
+          }
+        }
+      }
+    } else
 #pragma unroll
     for (int ch = 0; ch < 3; ++ch) {
-      // only window columns >= 256 of the last chunk are new: they sit in the last quarter
       if (ch == 2 && warp < 3) continue;
       const int c = chunk_start(ch) + 32 * warp + lane;
       const int j = b.jwin + c;
-      const bool use = (ch < 2 || c >= 256) && j >= 0 && j <= it.len - 1 - b.dmin;
+      const bool use = use3[ch];
       const int i_top = min(j + b.dmax, it.len - 1);
       const bool first = (b.w == it.w_begin) && (b.rb == i_top / kS2Rows);
       if (mask & 2) {
         float v[16];
         tc::tmem_ld16(tmem + lane_base + kColK + ch * NK, v);
         if (use) {
-          float* dst = a.dk_part + (it.rowslot + j) * D;
+          float* dst = dst_k[ch];
           if ((D & 3) == 0) {
 #pragma unroll
             for (int d4 = 0; d4 < 4; ++d4)
@@ -437,7 +495,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
           float v[16];
           tc::tmem_ld16(tmem + lane_base + kColV + ch * NV + n0, v);
           if (use && n0 < Dv) {
-            float* dst = a.dv_part + (it.rowslot + j + 1) * Dv + n0;
+            float* dst = dst_v[ch] + n0;
             if ((Dv & 3) == 0) {
 #pragma unroll
               for (int d4 = 0; d4 < 4; ++d4)
@@ -490,46 +548,104 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
   const int keep_word = tid >> 4, keep_shift = 2 * (tid & 15);
 
   // Tables of one block: column windows, row symbols and statistics, keep ballots, utility
-  // tables (scaled by ds_mul: the adjoint seed then needs no further factor) and the
-  // grad_output operand of the value sums.
-  auto fill_tables = [&](const S2Geom& g, unsigned char* bGhi, unsigned char* bGlo) {
-    for (int c = tid; c < kS2Win; c += kS2Threads) {
+  // tables (scaled by ds_mul: the adjoint seed then needs no further factor), the grad_output
+  // operand of the value sums and the thread's checkpoints.  They are fetched in two steps: the
+  // global loads of block b + 1 are issued into registers before the adjoint phase of block b
+  // and stored to shared memory after it, so their latency is never waited for.
+  constexpr int kColRegs = (kS2Win + kS2Threads - 1) / kS2Threads;        // 3
+  constexpr int kGoRegs = (NV * kS2Rows + kS2Threads - 1) / kS2Threads;   // 2 or 4
+  struct Prefetch {
+    int k[kColRegs], kold[kColRegs];
+    uint32_t vb[kColRegs];
+    int q, qold;
+    float4 st;
+    uint32_t keep;
+    uint32_t lut[4];       // raw grad_output elements of this thread's (row, value group)
+    uint32_t go[kGoRegs];  // raw grad_output elements of the operand tile
+    int4 ck;
+  };
+  auto go_bits = [&](int i, int d) -> uint32_t {
+    const int64_t idx = (((int64_t)it.start + i) * a.H + it.h) * Dv + d;
+    return a.dtype == ROSA_B200_F32 ? static_cast<const uint32_t*>(a.go)[idx]
+                                    : (uint32_t) static_cast<const uint16_t*>(a.go)[idx];
+  };
+  auto go_float = [&](uint32_t bits) {
+    if (a.dtype == ROSA_B200_F32) return __uint_as_float(bits);
+    if (a.dtype == ROSA_B200_F16) return __half2float(__ushort_as_half((unsigned short)bits));
+    return __uint_as_float(bits << 16);          // bf16 is the upper half of a float
+  };
+  auto prefetch_load = [&](const S2Geom& g, Prefetch& pf) {
+#pragma unroll
+    for (int x = 0; x < kColRegs; ++x) {
+      const int c = tid + x * kS2Threads;
       const int j = g.jwin + c;
-      const bool in = j >= 0 && j < it.len - 1;
-      s_k[c] = in ? __ldg(k + j) : 0;
+      const bool in = c < kS2Win && j >= 0 && j < it.len - 1;
+      pf.k[x] = in ? __ldg(k + j) : 0;
       const int jo = j - W - 1;
-      s_kold[c] = (windowed && jo >= 0 && jo < it.len) ? __ldg(k + jo) : 0;
-      const uint32_t bits = in ? __ldg(vb + j + 1) : 0u;
-      s_vb0[c] = spread_nibbles(bits & 0xffffu);
-      if (NG > 4) s_vb1[c] = spread_nibbles(bits >> 16);
+      pf.kold[x] = (windowed && c < kS2Win && jo >= 0 && jo < it.len) ? __ldg(k + jo) : 0;
+      pf.vb[x] = in ? __ldg(vb + j + 1) : 0u;
     }
+    pf.q = pf.qold = 0;
+    pf.st = make_float4(0.f, 0.f, 0.f, 0.f);
     if (tid < kS2Rows) {
       const int i = g.i0 + tid;
-      const bool in = i >= g.first_row && i <= it.len - 1;
-      s_q[tid] = in ? __ldg(q + i) : 0;
-      s_qold[tid] = (windowed && in && i - W - 1 >= 0) ? __ldg(q + i - W - 1) : 0;
-      float4 st = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (in) st = rowstat[i];                       // (max, 1/Z, E, log i)
-      s_rstat[tid] = make_float4(-(st.w + st.x) * kLog2e - mul2, st.y, st.z * ds_mul,
-                                 st.y * inv_keep);
+      if (i >= g.first_row && i <= it.len - 1) {
+        pf.q = __ldg(q + i);
+        if (windowed && i - W - 1 >= 0) pf.qold = __ldg(q + i - W - 1);
+        pf.st = rowstat[i];                          // (max, 1/Z, E, log i)
+      }
     }
+    pf.keep = 0u;
     if (kDropout) {
       const int r = tid >> 3, ro = r - g.skew;
-      s_keep[tid] = (ro >= 0 && g.i0 + r <= it.len - 1)
-                        ? a.keepbits[(g.ck_idx * kS2Rows + ro) * kVjpWarps + (tid & 7)]
-                        : 0u;
+      if (ro >= 0 && g.i0 + r <= it.len - 1)
+        pf.keep = a.keepbits[(g.ck_idx * kS2Rows + ro) * kVjpWarps + (tid & 7)];
     }
-    for (int e = tid; e < kS2Rows * NG; e += kS2Threads) {
-      const int r = e / NG, gq = e - r * NG;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) pf.lut[b] = 0u;
+    if (tid < kS2Rows * NG) {
+      const int r = tid / NG, gq = tid - r * NG;
       const int i = g.i0 + r;
-      float gv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       if (i >= g.first_row && i <= it.len - 1) {
-        const int64_t base = (((int64_t)it.start + i) * a.H + it.h) * Dv + 4 * gq;
 #pragma unroll
         for (int b = 0; b < 4; ++b)
-          if (4 * gq + b < Dv) gv[b] = ds_mul * load_as_float(a.go, base + b, a.dtype);
+          if (4 * gq + b < Dv) pf.lut[b] = go_bits(i, 4 * gq + b);
       }
-      float4* dst = reinterpret_cast<float4*>(ulut + e * 16);
+    }
+#pragma unroll
+    for (int x = 0; x < kGoRegs; ++x) {
+      const int e = tid + x * kS2Threads;
+      const int d = e / kS2Rows, r = e - d * kS2Rows;
+      const int i = g.i0 + r;
+      pf.go[x] = 0u;
+      if ((mask & 4) && e < NV * kS2Rows && d < Dv && i >= g.first_row && i <= it.len - 1)
+        pf.go[x] = go_bits(i, d);
+    }
+    pf.ck = *reinterpret_cast<const int4*>(a.ckpt + g.ck_idx * kS2Band + kS2R * tid);
+  };
+  auto prefetch_store = [&](const Prefetch& pf, unsigned char* bGhi, unsigned char* bGlo) {
+#pragma unroll
+    for (int x = 0; x < kColRegs; ++x) {
+      const int c = tid + x * kS2Threads;
+      if (c < kS2Win) {
+        s_k[c] = pf.k[x];
+        s_kold[c] = pf.kold[x];
+        s_vb0[c] = spread_nibbles(pf.vb[x] & 0xffffu);
+        if (NG > 4) s_vb1[c] = spread_nibbles(pf.vb[x] >> 16);
+      }
+    }
+    if (tid < kS2Rows) {
+      s_q[tid] = pf.q;
+      s_qold[tid] = pf.qold;
+      s_rstat[tid] = make_float4(-(pf.st.w + pf.st.x) * kLog2e - mul2, pf.st.y, pf.st.z * ds_mul,
+                                 pf.st.y * inv_keep);
+    }
+    if (kDropout) s_keep[tid] = pf.keep;
+    if (tid < kS2Rows * NG) {
+      float gv[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) gv[b] = ds_mul * go_float(pf.lut[b]);
+      float4* dst = reinterpret_cast<float4*>(ulut + tid * 16);
 #pragma unroll
       for (int n4 = 0; n4 < 4; ++n4) {
         const float hi = ((n4 & 1) ? gv[2] : -gv[2]) + ((n4 & 2) ? gv[3] : -gv[3]);
@@ -537,19 +653,21 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
                               hi + gv[0] + gv[1]);
       }
     }
-    if (mask & 4)
-      for (int e = tid; e < NV * kS2Rows; e += kS2Threads) {
-        const int d = e / kS2Rows, r = e - d * kS2Rows;
-        const int i = g.i0 + r;
-        float v = 0.0f;
-        if (d < Dv && i >= g.first_row && i <= it.len - 1)
-          v = load_as_float(a.go, (((int64_t)it.start + i) * a.H + it.h) * Dv + d, a.dtype);
-        const __nv_bfloat16 h = __float2bfloat16_rn(v);
-        *reinterpret_cast<__nv_bfloat16*>(bGhi + b_off(d, r, NV)) = h;
-        if (TM::glo)
-          *reinterpret_cast<__nv_bfloat16*>(bGlo + b_off(d, r, NV)) =
-              __float2bfloat16_rn(v - __bfloat162float(h));
+    if (mask & 4) {
+#pragma unroll
+      for (int x = 0; x < kGoRegs; ++x) {
+        const int e = tid + x * kS2Threads;
+        if (e < NV * kS2Rows) {
+          const int d = e / kS2Rows, r = e - d * kS2Rows;
+          const float v = go_float(pf.go[x]);
+          const __nv_bfloat16 h = __float2bfloat16_rn(v);
+          *reinterpret_cast<__nv_bfloat16*>(bGhi + b_off(d, r, NV)) = h;
+          if (TM::glo)
+            *reinterpret_cast<__nv_bfloat16*>(bGlo + b_off(d, r, NV)) =
+                __float2bfloat16_rn(v - __bfloat162float(h));
+        }
       }
+    }
   };
 
   int w = it.w_begin, rb = rb_top;
@@ -560,6 +678,13 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
   double Sbar[2] = {0.0, 0.0}, Y[2] = {0.0, 0.0};
   int live = 0;
   bool ring_dirty = false;
+  Prefetch pf;
+  {
+    prefetch_load(geom_of(w, rb), pf);
+    prefetch_store(pf, smem + L::oGhi, smem + L::oGlo);
+    __syncthreads();
+  }
+  int4 ck = pf.ck;
 
   while (true) {
     const S2Geom g = geom_of(w, rb);
@@ -582,10 +707,8 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
     unsigned char* bGhi = smem + L::oGhi + buf * L::kGBytes;
     unsigned char* bGlo = smem + L::oGlo + buf * L::kGBytes;
 
-    fill_tables(g, bGhi, bGlo);
-    const int4 ck = *reinterpret_cast<const int4*>(a.ckpt + g.ck_idx * kS2Band + kS2R * tid);
-    __syncthreads();                                   // sync 1: tables complete
-
+    (void)bGhi;
+    (void)bGlo;
     // ---- B operands that come from the tables
     if (mask & 2)
       for (int e = tid; e < NK * kS2Rows; e += kS2Threads) {
@@ -649,6 +772,9 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
         kow[0] = kow[4]; kow[1] = kow[5];
       }
     }
+
+    // ---- the next block's tables start their way from global memory now
+    if (has_next) prefetch_load(next_same ? geom_of(w, rb - 1) : geom_of(w + 1, rb_top), pf);
 
     // ---- the previous block's MMAs have had the whole table / forward phase to finish
     if (prev_pending) epilogue(prev_w, prev_rb);
@@ -760,6 +886,14 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
       }
     }
     (void)delta0;
+
+    // ---- the tables of the next block replace this block's once every warp is done with them
+    __syncthreads();
+    if (has_next) {
+      prefetch_store(pf, smem + L::oGhi + (buf ^ 1) * L::kGBytes,
+                     smem + L::oGlo + (buf ^ 1) * L::kGBytes);
+      ck = pf.ck;
+    }
 
     // ---- phase C: hand the operands to the tensor core
     tc::fence_proxy_async_smem();
