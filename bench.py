@@ -64,6 +64,8 @@ WORKLOADS = {
     # small cases for multi-pass profiler captures (scratch still larger than L2)
     "profile": dict(B=1, T=4096, H=32, D=8, Hv=8, Dv=8, W=128, scale=1.0, p=0.1, m=3.0,
                     dtype="bfloat16", gen="randn"),
+    "profile8k": dict(B=1, T=8192, H=32, D=8, Hv=8, Dv=8, W=128, scale=1.0, p=0.1, m=3.0,
+                      dtype="bfloat16", gen="randn"),
     "c3_profile": dict(B=1, T=4096, H=32, D=2, Hv=32, Dv=16, W=256, scale=1.0, p=0.0, m=3.0,
                        dtype="bfloat16", gen="repeat"),
     "c5_profile": dict(kind="inference", B=8, T=16384, H=64, D=32, Hv=64, Dv=8, W=32, scale=1.0,
@@ -78,7 +80,7 @@ SIDE_WORKLOADS = ("c2_f32", "c2_bf16", "c3", "c4", "c5", "stream")
 # DRAM bytes (read + write) of one launch of the backward's second sweep per causal pair, from
 # one ncu capture per kernel variant (profiles/); None where no capture backs a figure.
 SWEEP2_DRAM_BYTES_PER_PAIR = {"metric": None, "c2_bf16": None, "c2_f32": None, "c3": None,
-                              "c4": None, "profile": None, "small": None, "c3_profile": None}
+                              "c4": None, "profile": None, "profile8k": None, "small": None, "c3_profile": None}
 
 
 def describe(name, cfg):

@@ -68,11 +68,22 @@ __device__ __forceinline__ int window_sum_cutoff(float neg_md) {
   return lim < 1.0e9f ? (int)lim : 1000000000;
 }
 
-// Work item of a 1-D grid: heads vary fastest so that the longest bands of all heads are
-// scheduled first and the tail of the launch consists of the shortest bands.
+// Work item of a 1-D grid.  Heads vary fastest; for a dense batch the sequences vary next and
+// the item index slowest, so that the longest items (the bands next to the main diagonal) of ALL
+// sequences and heads are scheduled first and the tail of the launch consists of the shortest
+// ones (with the sequence slowest, the long items of the last sequences would start late and
+// finish alone).  Packed batches keep sequence-major order.
 __device__ __forceinline__ bool load_item_1d(const VjpArgs& a, Item* o) {
   const int slot = blockIdx.x / a.H;
-  if (!find_item(a.plan, slot, &o->seq, &o->it)) return false;
+  if (a.plan.cu_seqlens == nullptr) {
+    if (a.plan.status[0] != 0) return false;
+    const int per = a.plan.item_prefix[1];          // items of every sequence
+    if (per <= 0 || slot >= per * a.plan.S) return false;
+    o->it = slot / a.plan.S;
+    o->seq = slot - o->it * a.plan.S;
+  } else if (!find_item(a.plan, slot, &o->seq, &o->it)) {
+    return false;
+  }
   o->h = blockIdx.x - slot * a.H;
   o->start = a.plan.seg_start[o->seq];
   o->len = a.plan.seg_len[o->seq];

@@ -180,8 +180,10 @@ __device__ __forceinline__ uint32_t s1_group(const ColWindow<NG, kWindowed, kDro
       es[rr] += ex;
       if (kDropout) {
         const bool keep = act && dropout_keep_open(dkey, cw.h1[idx], qword);
-        keepbits |= (uint32_t)keep << (4 * rr + e);
-        eds[rr] += keep ? ex * du : 0.0f;
+        if (keep) {     // predicated: one logic operation and one fused multiply-add
+          keepbits |= 1u << (4 * rr + e);
+          eds[rr] = fmaf(ex, du, eds[rr]);
+        }
       } else {
         eds[rr] = fmaf(ex, du, eds[rr]);
       }

@@ -532,11 +532,20 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
       if (warp == 0 && lane < kS2Rows && i >= b.first_row && i <= it.len - 1) {
         float* dst = a.dq_part + (it.rowslot + i) * D;
 #pragma unroll
-        for (int d = 0; d < 16; ++d) {
-          float sum = v[d];
+        for (int d4 = 0; d4 < 4; ++d4) {
+          if (4 * d4 >= D) break;
+          float sum[4] = {v[4 * d4], v[4 * d4 + 1], v[4 * d4 + 2], v[4 * d4 + 3]};
 #pragma unroll
-          for (int t = 1; t < NC; ++t) sum += s_dq[((t - 1) * kS2Rows + lane) * 16 + d];
-          if (d < D) dst[d] = (b.w == it.w_begin) ? sum : dst[d] + sum;
+          for (int t = 1; t < NC; ++t) {
+            const float4 o =
+                *reinterpret_cast<const float4*>(s_dq + ((t - 1) * kS2Rows + lane) * 16 + 4 * d4);
+            sum[0] += o.x; sum[1] += o.y; sum[2] += o.z; sum[3] += o.w;
+          }
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const int d = 4 * d4 + x;
+            if (d < D) dst[d] = (b.w == it.w_begin) ? sum[x] : dst[d] + sum[x];
+          }
         }
       }
     }
