@@ -192,8 +192,9 @@ __device__ __forceinline__ uint32_t s1_group(const ColWindow<NG, kWindowed, kDro
   return keepbits;
 }
 
-// Sweep 1, four diagonals per thread.  Writes the same checkpoints, keep ballots and per-item
-// row partials as vjp_sweep1_kernel<NG, true, ...> (analytic softmax reference only).
+// Sweep 1, four diagonals per thread.  Writes the same checkpoints and per-item row partials as
+// vjp_sweep1_kernel<NG, true, ...> (analytic softmax reference only); the dropout keep flags go
+// out as one 64-bit word per thread and block, the layout vjp_sweep2_tiled_kernel reads.
 template <int NG, bool kWindowed, bool kDropout>
 __global__ void __launch_bounds__(kTThreads) vjp_sweep1_tiled_kernel(VjpArgs a) {
   extern __shared__ float4 smem_raw[];
@@ -293,7 +294,7 @@ __global__ void __launch_bounds__(kTThreads) vjp_sweep1_tiled_kernel(VjpArgs a) 
       const int col0 = kTBand - kTR - kTR * tid;
       ColWindow<NG, kWindowed, kDropout> cw;
       load_quad<NG, kWindowed, kDropout>(cw, sm, col0, 0);
-      uint32_t* keep_out = a.keepbits + (ck_idx * kTRows) * kVjpWarps;
+      uint32_t keep_lo = 0u, keep_hi = 0u;
 #pragma unroll 1
       for (int r0 = 0; r0 < kTRows; r0 += 4) {
         load_quad<NG, kWindowed, kDropout>(cw, sm, col0 + r0 + 4 < kTWin ? col0 + r0 + 4 : col0 + r0, 4);
@@ -308,18 +309,9 @@ __global__ void __launch_bounds__(kTThreads) vjp_sweep1_tiled_kernel(VjpArgs a) 
           keep = s1_group<NG, kWindowed, kDropout, true>(cw, sm, p, dkey, r0, i0, j_first, qword0, S,
                                                          hs, es, eds);
         if (kDropout) {
-          // keep ballots in the layout of the one-diagonal-per-thread kernels: one word per row
-          // and 32 diagonals, i.e. the nibbles of eight neighbouring threads
-#pragma unroll
-          for (int rr = 0; rr < 4; ++rr) {
-            uint32_t word = ((keep >> (4 * rr)) & 15u) << (4 * (lane & 7));
-            word |= __shfl_xor_sync(0xffffffffu, word, 1);
-            word |= __shfl_xor_sync(0xffffffffu, word, 2);
-            word |= __shfl_xor_sync(0xffffffffu, word, 4);
-            const int r = r0 + rr;
-            if ((lane & 7) == 0 && r >= skew && i0 + r <= it.len - 1)
-              keep_out[(r - skew) * kVjpWarps + (tid >> 3)] = word;
-          }
+          // 16 keep flags of this group: bit 4 r + e of the thread's 64-bit word of the block
+          if (r0 < 8) keep_lo |= keep << (4 * r0);
+          else keep_hi |= keep << (4 * (r0 - 8));
         }
         float v[8];
 #pragma unroll
@@ -340,6 +332,9 @@ __global__ void __launch_bounds__(kTThreads) vjp_sweep1_tiled_kernel(VjpArgs a) 
           if (NG > 4) cw.v1[x] = cw.v1[x + 4];
         }
       }
+      // keep flags of the block: one 64-bit word per thread (row r, diagonal e at bit 4 r + e)
+      if (kDropout)
+        reinterpret_cast<uint2*>(a.keepbits)[ck_idx * kTThreads + tid] = make_uint2(keep_lo, keep_hi);
       __syncthreads();
       if (tid < kTRows) {
         const int i = i0 + tid;

@@ -251,10 +251,12 @@ __device__ __forceinline__ bool s2_forward_group(const int* s_q, const int* s_qo
 // further down the diagonal.  Writes C and p*d into the operand area.
 template <int NG, int NC, int NP, bool kRound, bool kDropout, bool kEdge>
 __device__ __forceinline__ void s2_adjoint_group(
-    unsigned char* tC, unsigned char* tP, int cg, const float4* s_rstat, const uint32_t* s_keep,
+    unsigned char* tC, unsigned char* tP, int cg, const float4* s_rstat, uint2 keepw,
     const float* glut, const float* ulut, const uint32_t (&v0)[6], const uint32_t (&v1)[6],
     const float2* s_row, uint2 hamw, int r0, int i0, int j1, int len, int skew, int cb, float mul2,
-    int keep_word, int keep_shift, float (&sb)[2], float (&xnext)[2]) {
+    int keep_shift, float (&sb)[2], float (&xnext)[2]) {
+  // keep flags of the group's four rows, this thread's two diagonals at bits 4 rr, 4 rr + 1
+  const uint32_t kgroup = (r0 < 8 ? keepw.x : keepw.y) >> (4 * (r0 & 7) + keep_shift);
   // operand byte offsets of window columns cb .. cb + 4 (cb is even: cb + 1 and cb + 3 never
   // start a new group of eight columns)
   int o[5];
@@ -270,7 +272,7 @@ __device__ __forceinline__ void s2_adjoint_group(
     const float2 Sv = s_row[rr * kS2Threads];
     const uint32_t hb = rr < 2 ? hamw.x : hamw.y;
     uint32_t kbits = 3u;
-    if (kDropout) kbits = s_keep[r * kVjpWarps + keep_word] >> keep_shift;
+    if (kDropout) kbits = kgroup >> (4 * rr);
     float Cv[2], pd[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
@@ -329,7 +331,6 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
   uint32_t* s_vb1 = reinterpret_cast<uint32_t*>(smem + L::oVb1);
   int* s_q = reinterpret_cast<int*>(smem + L::oQ);
   int* s_qold = reinterpret_cast<int*>(smem + L::oQold);
-  uint32_t* s_keep = reinterpret_cast<uint32_t*>(smem + L::oKeep);
   float4* s_rstat = reinterpret_cast<float4*>(smem + L::oRstat);
   float* glut = reinterpret_cast<float*>(smem + L::oGlut);
   float* ulut = reinterpret_cast<float*>(smem + L::oUlut);
@@ -554,7 +555,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
 
   const int rb_top = (it.len - 1) / kS2Rows;     // bottom row block of every band
   const float inv_keep = a.inv_keep;
-  const int keep_word = tid >> 4, keep_shift = 2 * (tid & 15);
+  const int keep_shift = 2 * (tid & 1);
 
   // Tables of one block: column windows, row symbols and statistics, keep ballots, utility
   // tables (scaled by ds_mul: the adjoint seed then needs no further factor), the grad_output
@@ -568,7 +569,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
     uint32_t vb[kColRegs];
     int q, qold;
     float4 st;
-    uint32_t keep;
+    uint2 keep;            // keep flags of the sweep-1 thread that owns these two diagonals
     uint32_t lut[4];       // raw grad_output elements of this thread's (row, value group)
     uint32_t go[kGoRegs];  // raw grad_output elements of the operand tile
     int4 ck;
@@ -604,12 +605,9 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
         pf.st = rowstat[i];                          // (max, 1/Z, E, log i)
       }
     }
-    pf.keep = 0u;
-    if (kDropout) {
-      const int r = tid >> 3, ro = r - g.skew;
-      if (ro >= 0 && g.i0 + r <= it.len - 1)
-        pf.keep = a.keepbits[(g.ck_idx * kS2Rows + ro) * kVjpWarps + (tid & 7)];
-    }
+    pf.keep = make_uint2(0u, 0u);
+    if (kDropout)   // word of sweep-1 thread tid / 2: row r, diagonal e of that thread at bit 4 r + e
+      pf.keep = reinterpret_cast<const uint2*>(a.keepbits)[g.ck_idx * (kS2Band / 4) + (tid >> 1)];
 #pragma unroll
     for (int b = 0; b < 4; ++b) pf.lut[b] = 0u;
     if (tid < kS2Rows * NG) {
@@ -649,7 +647,6 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
       s_rstat[tid] = make_float4(-(pf.st.w + pf.st.x) * kLog2e - mul2, pf.st.y, pf.st.z * ds_mul,
                                  pf.st.y * inv_keep);
     }
-    if (kDropout) s_keep[tid] = pf.keep;
     if (tid < kS2Rows * NG) {
       float gv[4];
 #pragma unroll
@@ -694,6 +691,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
     __syncthreads();
   }
   int4 ck = pf.ck;
+  uint2 keepw = pf.keep;
 
   while (true) {
     const S2Geom g = geom_of(w, rb);
@@ -810,15 +808,13 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
         const uint2 hamw = Hbuf[(r0 >> 2) * kS2Threads + tid];
         const int j1 = g.jwin + cb;
         if (interior)
-          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, false>(tC, tP, CG, s_rstat, s_keep, glut, ulut, v0,
+          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, false>(tC, tP, CG, s_rstat, keepw, glut, ulut, v0,
                                                         v1, s_row, hamw, r0, g.i0, j1, it.len,
-                                                        g.skew, cb, mul2, keep_word, keep_shift,
-                                                        sb, xnext);
+                                                        g.skew, cb, mul2, keep_shift, sb, xnext);
         else
-          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, true>(tC, tP, CG, s_rstat, s_keep, glut, ulut, v0,
+          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, true>(tC, tP, CG, s_rstat, keepw, glut, ulut, v0,
                                                        v1, s_row, hamw, r0, g.i0, j1, it.len,
-                                                       g.skew, cb, mul2, keep_word, keep_shift, sb,
-                                                       xnext);
+                                                       g.skew, cb, mul2, keep_shift, sb, xnext);
       }
       Sbar[0] = (double)sb[0];
       Sbar[1] = (double)sb[1];
@@ -835,7 +831,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
         const uint2 hamw = Hbuf[(r >> 2) * kS2Threads + tid];
         const uint32_t hb = (r & 3) < 2 ? hamw.x : hamw.y;
         uint32_t kbits = 3u;
-        if (kDropout) kbits = s_keep[r * kVjpWarps + keep_word] >> keep_shift;
+        if (kDropout) kbits = (r < 8 ? keepw.x : keepw.y) >> (4 * (r & 7) + keep_shift);
         const int qo = s_qold[r];
         float Cv[2], pd[2], Pv[2], gate[2], dS[2];
         bool act[2];
@@ -903,6 +899,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
                      smem + L::oGlo + (buf ^ 1) * L::kGBytes);
       ck = pf.ck;
     }
+    keepw = pf.keep;
 
     // ---- phase C: hand the operands to the tensor core
     tc::fence_proxy_async_smem();
