@@ -102,7 +102,12 @@ VjpLayout vjp_layout(int64_t N, int H, int D, int Hv, int Dv, int64_t S, int64_t
   int64_t items = 0, rows = 0, cks = 0;
   for (;; g *= 2) {
     vjp_bounds(N, S, uniform_len, dense, (int64_t)g * kVjpBand, &items, &rows, &cks);
-    if ((size_t)rows * H * per_row <= kPartialBudgetBytes || (int64_t)g * kVjpBand >= max_len) break;
+    // the window ring (one line of kVjpBand floats per horizon step and item) counts against
+    // the same budget: fewer, longer items shrink it together with the partial rows
+    const size_t ring = (size_t)items * H * l.ring_slots * kVjpBand * sizeof(float);
+    if ((size_t)rows * H * per_row + ring <= kPartialBudgetBytes ||
+        (int64_t)g * kVjpBand >= max_len)
+      break;
   }
   l.bands_per_item = g;
   l.items_upper = items;
@@ -371,7 +376,8 @@ ROSA_B200_API int rosa_b200_surrogate_vjp(const void* query, const void* key, co
   const VjpLayout l = vjp_layout(N, H, D, Hv, Dv, num_seq, uniform_len, dense, W, gradient_mask);
   ROSA_REQUIRE(workspace_bytes >= l.bytes, "workspace too small: need %zu bytes, got %zu", l.bytes,
                workspace_bytes);
-  ROSA_REQUIRE(l.items_upper <= std::numeric_limits<int32_t>::max(), "too many work items");
+  ROSA_REQUIRE(l.items_upper * (int64_t)H <= std::numeric_limits<int32_t>::max(),
+               "too many work items: items * heads exceeds the CUDA grid limit");
   cudaStream_t st = as_stream(stream);
   char* ws = static_cast<char*>(workspace);
 

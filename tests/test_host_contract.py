@@ -169,3 +169,23 @@ def test_runtime_constructor_and_input_contract_without_a_gpu():
     rt.close()
     with pytest.raises(RuntimeError, match="closed"):
         rt.reset()
+
+
+def test_installer_honours_the_reference_build_switches():
+    """ROSA_BUILD_EXTENSION / USE_CUDA as in the reference's setup.py:50-96; the variants this
+    package does not have are refused instead of installed half."""
+    import types
+    source = open(os.path.join(ROOT, "setup.py")).read()
+    # run the script with `setup(...)` made a no-op: only its helpers are wanted here
+    source = source.replace("from setuptools import setup\n", "setup = lambda **kw: None\n")
+    module = types.ModuleType("_rosa_setup")
+    module.__file__ = os.path.join(ROOT, "setup.py")
+    exec(compile(source, module.__file__, "exec"), module.__dict__)
+    assert module.resolve_variant({}) == "cuda"
+    assert module.resolve_variant({"USE_CUDA": "1", "ROSA_BUILD_EXTENSION": "1"}) == "cuda"
+    for env in ({"ROSA_BUILD_EXTENSION": "0"}, {"USE_CUDA": "0"}):
+        with pytest.raises(RuntimeError, match="only exists as the CUDA variant"):
+            module.resolve_variant(env)
+    with pytest.raises(RuntimeError, match="USE_CUDA must be"):
+        module.resolve_variant({"USE_CUDA": "maybe"})
+    assert module._version() == "0.1.0"
