@@ -76,6 +76,29 @@ ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, con
                            int32_t* route_token /* nullable, [N, H] */, void* workspace,
                            size_t workspace_bytes, void* stream);
 
+/* The two halves of the forward for a caller that fuses its neighbours (the Q/K projections
+ * that feed the operator and the output projection that consumes it, reference
+ * examples/fit_soft_reference.py:374-415).
+ * rosa_b200_pack_symbols is the contract of the projection epilogue: bit d of the int32 word of
+ * (token, head) is set iff logit d is strictly positive (+0, -0 and NaN give 0; reference
+ * rosa_soft/csrc/cuda/rosa_soft_kernels.cu:229-240), words laid out [num_seq, H, uniform_len]
+ * (dense, uniform_len > 0) or [H, N] (packed, uniform_len = 0).  A GEMM epilogue that writes
+ * these words never has to materialise the logits; this entry point does the same from logits
+ * in memory, for one tensor.
+ * rosa_b200_hard_forward_packed then runs matching and gathering on symbols the caller already
+ * holds (no packing pass, the symbol tensors are inputs) and writes the routed signs as int8
+ * -1 / 0 / +1 [N, H, Dv] for a consumer that takes them as integers.  Same workspace size, status
+ * word and route_token output as rosa_b200_hard_forward; `D` is the symbol width in bits. */
+ROSA_B200_API int rosa_b200_pack_symbols(const void* logits, int dtype, int64_t N, int H, int D,
+                                         int64_t num_seq, int64_t uniform_len, int32_t* packed,
+                                         void* stream);
+
+ROSA_B200_API int rosa_b200_hard_forward_packed(
+    const int32_t* packed_query, const int32_t* packed_key, const void* value, int dtype, int64_t N,
+    int H, int D, int Hv, int Dv, const int32_t* cu_seqlens, int64_t num_seq, int64_t uniform_len,
+    int64_t max_suffix_length, int8_t* output, int32_t* route_token /* nullable, [N, H] */,
+    void* workspace, size_t workspace_bytes, void* stream);
+
 /* Hard forward without a workspace argument (no counterpart in the reference, whose
  * operators always allocate through the framework).  For hosts that cannot allocate device
  * memory at call time -- a server that gave all of it to its own arena and keeps the CUDA

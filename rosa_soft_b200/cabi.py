@@ -20,6 +20,8 @@ EXPORTED_SYMBOLS = (
     "rosa_b200_hard_forward_workspace_bytes",
     "rosa_b200_hard_forward",
     "rosa_b200_hard_forward_static",
+    "rosa_b200_pack_symbols",
+    "rosa_b200_hard_forward_packed",
     "rosa_b200_hard_forward_routes",
     "rosa_b200_surrogate_vjp_workspace_bytes",
     "rosa_b200_surrogate_vjp",
@@ -55,6 +57,11 @@ def load() -> ctypes.CDLL:
     lib.rosa_b200_hard_forward_static.restype = i32
     lib.rosa_b200_hard_forward_static.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, i32, vp, i64,
                                                   i64, i64, vp, vp, vp, vp, vp]
+    lib.rosa_b200_pack_symbols.restype = i32
+    lib.rosa_b200_pack_symbols.argtypes = [vp, i32, i64, i32, i32, i64, i64, vp, vp]
+    lib.rosa_b200_hard_forward_packed.restype = i32
+    lib.rosa_b200_hard_forward_packed.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, i32, vp, i64,
+                                                  i64, i64, vp, vp, vp, sz, vp]
     lib.rosa_b200_hard_forward_routes.restype = i32
     lib.rosa_b200_hard_forward_routes.argtypes = [vp, sz, i64, i32, i64, vp, vp, vp]
     lib.rosa_b200_surrogate_vjp_workspace_bytes.restype = sz
@@ -146,6 +153,49 @@ def hard_forward(q, k, v, cu_seqlens, max_suffix_length, want_routes=True, strea
                                      _ptr(pq), _ptr(pk), _ptr(routes), _ptr(ws), nbytes,
                                      ctypes.c_void_p(st)))
     return out, pq, pk, routes, ws
+
+
+def pack_symbols(x, cu_seqlens, stream=None):
+    """Sign bits of logits x [N, H, D] as int32 words in the operator's symbol layout: [S, H, T]
+    for a dense batch (``cu_seqlens=(S, T)``), [H, N] otherwise."""
+    import torch
+
+    N, H, D = x.shape
+    if isinstance(cu_seqlens, tuple):
+        S, T = cu_seqlens
+        out = torch.empty((S, H, T), dtype=torch.int32, device=x.device)
+    else:
+        S, T = cu_seqlens.numel() - 1, 0
+        out = torch.empty((H, N), dtype=torch.int32, device=x.device)
+    st = stream if stream is not None else torch.cuda.current_stream(x.device).cuda_stream
+    check(load().rosa_b200_pack_symbols(_ptr(x), dtype_code(x.dtype), N, H, D, S, T, _ptr(out),
+                                        ctypes.c_void_p(st)))
+    return out
+
+
+def hard_forward_packed(packed_q, packed_k, v, bits, cu_seqlens, max_suffix_length, stream=None):
+    """Forward on symbols the caller already holds; returns (int8 output [N, H, Dv], route_token,
+    workspace)."""
+    import torch
+
+    lib = load()
+    N, Hv, Dv = v.shape
+    if isinstance(cu_seqlens, tuple):
+        S, T = cu_seqlens
+        H, cu = packed_q.shape[1], None
+    else:
+        S, T = cu_seqlens.numel() - 1, 0
+        H, cu = packed_q.shape[0], cu_seqlens
+    out = torch.empty((N, H, Dv), dtype=torch.int8, device=v.device)
+    routes = torch.empty((N, H), dtype=torch.int32, device=v.device)
+    nbytes = lib.rosa_b200_hard_forward_workspace_bytes(N, H, S)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=v.device)
+    st = stream if stream is not None else torch.cuda.current_stream(v.device).cuda_stream
+    check(lib.rosa_b200_hard_forward_packed(_ptr(packed_q), _ptr(packed_k), _ptr(v),
+                                            dtype_code(v.dtype), N, H, int(bits), Hv, Dv, _ptr(cu),
+                                            S, T, int(max_suffix_length), _ptr(out), _ptr(routes),
+                                            _ptr(ws), nbytes, ctypes.c_void_p(st)))
+    return out, routes, ws
 
 
 def hard_forward_routes(ws, N, H, num_seq, stream=None):

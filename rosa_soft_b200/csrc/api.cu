@@ -172,21 +172,28 @@ ROSA_B200_API size_t rosa_b200_hard_forward_workspace_bytes(int64_t N, int H, in
   return fwd_layout(N, H, num_seq, false).bytes;
 }
 
-ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, const void* value, int dtype,
-                           int64_t N, int H, int D, int Hv, int Dv, const int32_t* cu_seqlens,
-                           int64_t num_seq, int64_t uniform_len, int64_t max_suffix_length,
-                           void* output, int32_t* packed_query, int32_t* packed_key,
-                           int32_t* route_token, void* workspace, size_t workspace_bytes,
-                           void* stream) {
+namespace {
+// Shared driver of the two forward entry points.  `query` / `key` null: the packed symbols are
+// inputs (already produced by the caller, e.g. by the epilogue of its projection GEMM) and the
+// packing kernel is skipped.  `output_i8` non-null: the routed signs go out as int8.
+int run_hard_forward(const void* query, const void* key, const void* value, int dtype, int64_t N,
+                     int H, int D, int Hv, int Dv, const int32_t* cu_seqlens, int64_t num_seq,
+                     int64_t uniform_len, int64_t max_suffix_length, void* output,
+                     int8_t* output_i8, int32_t* packed_query, int32_t* packed_key,
+                     int32_t* route_token, void* workspace, size_t workspace_bytes, void* stream) {
   if (int rc = check_problem(N, H, D, Hv, Dv, cu_seqlens, num_seq, uniform_len, max_suffix_length,
                              dtype))
     return rc;
-  ROSA_REQUIRE(query && key && value && output && packed_query && packed_key && workspace,
+  ROSA_REQUIRE(value && (output || output_i8) && packed_query && packed_key && workspace,
                "null pointer argument");
+  ROSA_REQUIRE((query == nullptr) == (key == nullptr), "query and key go together");
   const bool dense = cu_seqlens == nullptr;
   const FwdLayout l = fwd_layout(N, H, num_seq, false);
   ROSA_REQUIRE(workspace_bytes >= l.bytes, "workspace too small: need %zu bytes, got %zu", l.bytes,
                workspace_bytes);
+  const int64_t items = fwd_items_upper(N, num_seq, uniform_len, dense);
+  ROSA_REQUIRE(items * (int64_t)H <= std::numeric_limits<int32_t>::max(),
+               "too many work items: items * heads exceeds the CUDA grid limit");
   cudaStream_t st = as_stream(stream);
   char* ws = static_cast<char*>(workspace);
 
@@ -195,7 +202,8 @@ ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, con
   a.q = query; a.k = key; a.v = value; a.dtype = dtype;
   a.N = N; a.H = H; a.D = D; a.Hv = Hv; a.Dv = Dv;
   a.W = (int)std::min<int64_t>(max_suffix_length, dense ? uniform_len : N);
-  a.out = output; a.packed_q = packed_query; a.packed_k = packed_key;
+  a.out = output; a.out_i8 = output_i8;
+  a.packed_q = packed_query; a.packed_k = packed_key;
   a.route_token = route_token;
   a.best = reinterpret_cast<unsigned long long*>(ws + l.best_off);
   a.sym_seq_stride = dense ? (int64_t)H * uniform_len : 0;
@@ -211,12 +219,54 @@ ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, con
   launch_build_plan(a.plan, st);
   ROSA_CUDA_OK(cudaGetLastError());
   ROSA_CUDA_OK(cudaMemsetAsync(a.best, 0, (size_t)N * H * sizeof(unsigned long long), st));
-  if (int rc = launch_pack_symbols(query, key, dtype, N, H, D, dense, uniform_len, packed_query,
-                                   packed_key, st))
-    return rc;
-  if (int rc = launch_hard_match(a, (int)fwd_items_upper(N, num_seq, uniform_len, dense), st))
-    return rc;
+  if (query != nullptr)
+    if (int rc = launch_pack_symbols(query, key, dtype, N, H, D, dense, uniform_len, packed_query,
+                                     packed_key, st))
+      return rc;
+  if (int rc = launch_hard_match(a, (int)items, st)) return rc;
   return launch_gather_output(a, st);
+}
+}  // namespace
+
+ROSA_B200_API int rosa_b200_hard_forward(const void* query, const void* key, const void* value, int dtype,
+                           int64_t N, int H, int D, int Hv, int Dv, const int32_t* cu_seqlens,
+                           int64_t num_seq, int64_t uniform_len, int64_t max_suffix_length,
+                           void* output, int32_t* packed_query, int32_t* packed_key,
+                           int32_t* route_token, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  if (int rc = check_problem(N, H, D, Hv, Dv, cu_seqlens, num_seq, uniform_len, max_suffix_length,
+                             dtype))
+    return rc;
+  ROSA_REQUIRE(query && key && output, "null pointer argument");
+  return run_hard_forward(query, key, value, dtype, N, H, D, Hv, Dv, cu_seqlens, num_seq,
+                          uniform_len, max_suffix_length, output, nullptr, packed_query, packed_key,
+                          route_token, workspace, workspace_bytes, stream);
+}
+
+ROSA_B200_API int rosa_b200_pack_symbols(const void* logits, int dtype, int64_t N, int H, int D,
+                                         int64_t num_seq, int64_t uniform_len, int32_t* packed,
+                                         void* stream) {
+  ROSA_REQUIRE(dtype >= ROSA_B200_F32 && dtype <= ROSA_B200_BF16,
+               "dtype must be float32, float16 or bfloat16");
+  ROSA_REQUIRE(logits && packed, "null pointer argument");
+  ROSA_REQUIRE(N > 0 && H > 0 && D >= 1 && D <= 32, "invalid problem size");
+  const bool dense = uniform_len > 0;
+  if (dense)
+    ROSA_REQUIRE(num_seq * uniform_len == N, "dense description needs num_seq * uniform_len == N");
+  return launch_pack_symbols(logits, nullptr, dtype, N, H, D, dense, uniform_len, packed, nullptr,
+                             as_stream(stream));
+}
+
+ROSA_B200_API int rosa_b200_hard_forward_packed(
+    const int32_t* packed_query, const int32_t* packed_key, const void* value, int dtype, int64_t N,
+    int H, int D, int Hv, int Dv, const int32_t* cu_seqlens, int64_t num_seq, int64_t uniform_len,
+    int64_t max_suffix_length, int8_t* output, int32_t* route_token, void* workspace,
+    size_t workspace_bytes, void* stream) {
+  ROSA_REQUIRE(packed_query && packed_key && output, "null pointer argument");
+  return run_hard_forward(nullptr, nullptr, value, dtype, N, H, D, Hv, Dv, cu_seqlens, num_seq,
+                          uniform_len, max_suffix_length, nullptr, output,
+                          const_cast<int32_t*>(packed_query), const_cast<int32_t*>(packed_key),
+                          route_token, workspace, workspace_bytes, stream);
 }
 
 ROSA_B200_API int rosa_b200_hard_forward_routes(const void* workspace, size_t workspace_bytes,

@@ -267,6 +267,7 @@ struct FwdArgs {
   int H, D, Hv, Dv;
   int W;
   void* out;
+  int8_t* out_i8;      // when set, the routed signs are written as -1 / 0 / +1 bytes instead
   int32_t* packed_q;   // head-major symbols (operator output)
   int32_t* packed_k;
   int32_t* route_token;           // optional

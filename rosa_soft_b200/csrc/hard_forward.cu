@@ -29,22 +29,38 @@ __device__ __forceinline__ bool positive<__nv_bfloat16>(__nv_bfloat16 x) {
   return __bfloat162float(x) > 0.0f;
 }
 
+// Sign bits of one D-vector.  When the vector is a whole number of 16-byte words (and the tensor
+// base is 16-byte aligned) it is read with 128-bit loads; bit d of the word is set iff
+// component d is strictly positive (zero, -0 and NaN give 0).
+template <typename T>
+__device__ __forceinline__ uint32_t sign_word(const T* __restrict__ row, int D, bool vec) {
+  uint32_t w = 0;
+  if (vec) {
+    constexpr int kPer = 16 / (int)sizeof(T);
+    const uint4* p = reinterpret_cast<const uint4*>(row);
+    for (int c = 0; c < D / kPer; ++c) {
+      const uint4 raw = __ldg(p + c);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int x = 0; x < kPer; ++x) w |= (uint32_t)positive<T>(e[x]) << (c * kPer + x);
+    }
+  } else {
+    for (int d = 0; d < D; ++d) w |= (uint32_t)positive<T>(row[d]) << d;
+  }
+  return w;
+}
+
 // One thread per (token, head); threads of a warp read consecutive D-vectors.
 template <typename T>
 __global__ void pack_symbols_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t N,
-                                    int H, int D, int dense, int64_t uniform_len,
+                                    int H, int D, int dense, int64_t uniform_len, int vec,
                                     int32_t* __restrict__ pq, int32_t* __restrict__ pk) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= N * H) return;
   const int64_t token = idx / H;
   const int h = (int)(idx - token * H);
-  const T* qr = q + idx * D;
-  const T* kr = k + idx * D;
-  uint32_t wq = 0, wk = 0;
-  for (int d = 0; d < D; ++d) {
-    wq |= (uint32_t)positive<T>(qr[d]) << d;
-    wk |= (uint32_t)positive<T>(kr[d]) << d;
-  }
+  const uint32_t wq = sign_word<T>(q + idx * D, D, vec != 0);
+  const uint32_t wk = k != nullptr ? sign_word<T>(k + idx * D, D, vec != 0) : 0u;
   int64_t dst;
   if (dense) {
     const int64_t b = token / uniform_len, t = token - b * uniform_len;
@@ -53,7 +69,7 @@ __global__ void pack_symbols_kernel(const T* __restrict__ q, const T* __restrict
     dst = (int64_t)h * N + token;
   }
   pq[dst] = (int32_t)wq;
-  pk[dst] = (int32_t)wk;
+  if (k != nullptr) pk[dst] = (int32_t)wk;
 }
 
 // token-major [N, H] symbols -> head-major [H, N]
@@ -397,24 +413,16 @@ __global__ void __launch_bounds__(kBitsWarps * 32)
 }
 
 // ------------------------------------------------------------------- gather
-template <typename T>
-__device__ __forceinline__ T from_float(float x);
-template <>
-__device__ __forceinline__ float from_float<float>(float x) { return x; }
-template <>
-__device__ __forceinline__ __half from_float<__half>(float x) { return __float2half(x); }
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
-  return __float2bfloat16(x);
-}
-
-// One thread per (token, head, chunk of kChunk value components).
-template <typename T>
+// One thread per (token, head, chunk of value components): 16 bytes of output per thread when
+// the rows allow it (128-bit loads of the value row, one 128-bit store), else element by element.
+// OutT = T writes the operator's output in the input dtype; OutT = int8_t writes -1 / 0 / +1
+// bytes for a consumer that takes the routed signs as integers.
+template <typename T, typename OutT>
 __global__ void gather_output_kernel(Plan plan, const unsigned long long* __restrict__ best,
                                      const T* __restrict__ v, int64_t N, int H, int Hv, int Dv,
-                                     T* __restrict__ out, int32_t* __restrict__ route_token) {
-  constexpr int kChunk = 8;
-  const int chunks = (Dv + kChunk - 1) / kChunk;
+                                     int chunk, int vec, OutT* __restrict__ out,
+                                     int32_t* __restrict__ route_token) {
+  const int chunks = (Dv + chunk - 1) / chunk;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= N * H * chunks) return;
   const int c = (int)(idx % chunks);
@@ -426,14 +434,31 @@ __global__ void gather_output_kernel(Plan plan, const unsigned long long* __rest
   int64_t src_token = -1;
   if (route > 0 && find_segment(plan, token, &start, &len) >= 0) src_token = (int64_t)start + route;
   if (c == 0 && route_token) route_token[th] = (int32_t)src_token;
-  T* o = out + th * Dv;
-  const int d0 = c * kChunk, d1 = min(Dv, d0 + kChunk);
-  if (src_token < 0) {
-    for (int d = d0; d < d1; ++d) o[d] = from_float<T>(0.0f);
-  } else {
-    const T* src = v + (src_token * Hv + h / (H / Hv)) * Dv;
-    for (int d = d0; d < d1; ++d) o[d] = from_float<T>(positive<T>(src[d]) ? 1.0f : -1.0f);
+  OutT* o = out + th * Dv;
+  const int d0 = c * chunk, d1 = min(Dv, d0 + chunk);
+  const T* src = src_token < 0 ? nullptr : v + (src_token * Hv + h / (H / Hv)) * Dv;
+  if (vec) {
+    // `chunk` components: 16 bytes of OutT; the value row is read in 16-byte words
+    constexpr int kOutPer = 16 / (int)sizeof(OutT);
+    constexpr int kInPer = 16 / (int)sizeof(T);
+    alignas(16) OutT vals[kOutPer];
+#pragma unroll
+    for (int x = 0; x < kOutPer; ++x) vals[x] = (OutT)0;
+    if (src != nullptr) {
+#pragma unroll
+      for (int wd = 0; wd < kOutPer / kInPer; ++wd) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + d0) + wd);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int x = 0; x < kInPer; ++x)
+          vals[wd * kInPer + x] = positive<T>(e[x]) ? (OutT)1.0f : (OutT)-1.0f;
+      }
+    }
+    *reinterpret_cast<uint4*>(o + d0) = *reinterpret_cast<const uint4*>(vals);
+    return;
   }
+  for (int d = d0; d < d1; ++d)
+    o[d] = src == nullptr ? (OutT)0 : positive<T>(src[d]) ? (OutT)1.0f : (OutT)-1.0f;
 }
 
 __global__ void inference_finish_kernel(Plan plan, const unsigned long long* __restrict__ best,
@@ -487,15 +512,18 @@ int launch_pack_symbols(const void* q, const void* k, int dtype, int64_t N, int 
   ProfileScope prof("pack_symbols", stream);
   const int threads = 256;
   const int64_t blocks = (N * H + threads - 1) / threads;
+  const int esize = dtype == ROSA_B200_F32 ? 4 : 2;
+  const auto aligned = [](const void* p) { return p == nullptr || ((uintptr_t)p & 15u) == 0; };
+  const int vec = (D * esize) % 16 == 0 && aligned(q) && aligned(k);
   if (dtype == ROSA_B200_F32)
     pack_symbols_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
-        (const float*)q, (const float*)k, N, H, D, dense, uniform_len, pq, pk);
+        (const float*)q, (const float*)k, N, H, D, dense, uniform_len, vec, pq, pk);
   else if (dtype == ROSA_B200_F16)
     pack_symbols_kernel<__half><<<(unsigned)blocks, threads, 0, stream>>>(
-        (const __half*)q, (const __half*)k, N, H, D, dense, uniform_len, pq, pk);
+        (const __half*)q, (const __half*)k, N, H, D, dense, uniform_len, vec, pq, pk);
   else
     pack_symbols_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, N, H, D, dense, uniform_len, pq, pk);
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, N, H, D, dense, uniform_len, vec, pq, pk);
   ROSA_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -577,24 +605,36 @@ int launch_hard_match(const FwdArgs& a, int items_upper, cudaStream_t stream) {
   return 0;
 }
 
-int launch_gather_output(const FwdArgs& a, cudaStream_t stream) {
-  ProfileScope prof("gather_output", stream);
-  const int chunks = (a.Dv + 7) / 8;
+namespace {
+template <typename T, typename OutT>
+int launch_gather_t(const FwdArgs& a, OutT* out, cudaStream_t stream) {
+  // vector path: a thread writes 16 bytes of output, i.e. 16 / sizeof(OutT) components, and
+  // reads as many value components in 16-byte words
+  constexpr int kOutPer = 16 / (int)sizeof(OutT);
+  const auto aligned = [](const void* p) { return ((uintptr_t)p & 15u) == 0; };
+  const bool vec = a.Dv % kOutPer == 0 && aligned(a.v) && aligned(out) &&
+                   (a.Dv * (int)sizeof(T)) % 16 == 0 && kOutPer >= 16 / (int)sizeof(T);
+  const int chunk = vec ? kOutPer : 8;
+  const int chunks = (a.Dv + chunk - 1) / chunk;
   const int threads = 256;
-  const int64_t total = a.N * a.H * chunks;
-  const int64_t blocks = (total + threads - 1) / threads;
-  if (a.dtype == ROSA_B200_F32)
-    gather_output_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
-        a.plan, a.best, (const float*)a.v, a.N, a.H, a.Hv, a.Dv, (float*)a.out, a.route_token);
-  else if (a.dtype == ROSA_B200_F16)
-    gather_output_kernel<__half><<<(unsigned)blocks, threads, 0, stream>>>(
-        a.plan, a.best, (const __half*)a.v, a.N, a.H, a.Hv, a.Dv, (__half*)a.out, a.route_token);
-  else
-    gather_output_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
-        a.plan, a.best, (const __nv_bfloat16*)a.v, a.N, a.H, a.Hv, a.Dv, (__nv_bfloat16*)a.out,
-        a.route_token);
+  const int64_t blocks = (a.N * a.H * chunks + threads - 1) / threads;
+  gather_output_kernel<T, OutT><<<(unsigned)blocks, threads, 0, stream>>>(
+      a.plan, a.best, (const T*)a.v, a.N, a.H, a.Hv, a.Dv, chunk, vec ? 1 : 0, out, a.route_token);
   ROSA_CUDA_OK(cudaGetLastError());
   return 0;
+}
+}  // namespace
+
+int launch_gather_output(const FwdArgs& a, cudaStream_t stream) {
+  ProfileScope prof("gather_output", stream);
+  if (a.out_i8 != nullptr) {
+    if (a.dtype == ROSA_B200_F32) return launch_gather_t<float, int8_t>(a, a.out_i8, stream);
+    if (a.dtype == ROSA_B200_F16) return launch_gather_t<__half, int8_t>(a, a.out_i8, stream);
+    return launch_gather_t<__nv_bfloat16, int8_t>(a, a.out_i8, stream);
+  }
+  if (a.dtype == ROSA_B200_F32) return launch_gather_t<float, float>(a, (float*)a.out, stream);
+  if (a.dtype == ROSA_B200_F16) return launch_gather_t<__half, __half>(a, (__half*)a.out, stream);
+  return launch_gather_t<__nv_bfloat16, __nv_bfloat16>(a, (__nv_bfloat16*)a.out, stream);
 }
 
 int launch_inference_finish(const Plan& plan, const unsigned long long* best, const float* payload,
