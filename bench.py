@@ -79,8 +79,15 @@ SIDE_WORKLOADS = ("c2_f32", "c2_bf16", "c3", "c4", "c5", "stream")
 
 # DRAM bytes (read + write) of one launch of the backward's second sweep per causal pair, from
 # one ncu capture per kernel variant (profiles/); None where no capture backs a figure.
-SWEEP2_DRAM_BYTES_PER_PAIR = {"metric": None, "c2_bf16": None, "c2_f32": None, "c3": None,
-                              "c4": None, "profile": None, "profile8k": None, "small": None, "c3_profile": None}
+SWEEP2_DRAM_BYTES_PER_PAIR = {
+    # vjp_sweep2_tiled_kernel<16,2,true,2> on `profile8k`: 1103.7 MB for 1073.6 M pairs
+    # (profiles/vjp_sweep2_tiled__profile8k_T8192_H32.md); same kernel and controls
+    "metric": 1.028, "profile8k": 1.028, "profile": 1.028, "small": 1.028, "c2_bf16": 1.028,
+    # vjp_sweep2_tiled_kernel<16,4,false,2> on `c3_profile`: 218.8 MB for 268.4 M pairs (same file)
+    "c3": 0.815, "c3_profile": 0.815,
+    # no capture of the float32 / float16 variants: no figure
+    "c2_f32": None, "c4": None,
+}
 
 
 def describe(name, cfg):

@@ -835,6 +835,11 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
         const int qo = s_qold[r];
         float Cv[2], pd[2], Pv[2], gate[2], dS[2];
         bool act[2];
+        // the ring line of this row is requested first: while no window product has been alive
+        // for W + 2 rows the ring holds zeros and nothing is read
+        float* line = ring + (int64_t)(i % ring_slots) * kS2Band;
+        float2 old_t = make_float2(0.0f, 0.0f);
+        if (live > 0) old_t = *reinterpret_cast<const float2*>(line);
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int c = r + kS2Band - 1 - kS2R * tid - e;
@@ -862,12 +867,11 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a)
           ring_dirty = true;
         }
         if (live > 0) {
-          float* line = ring + (int64_t)(i % ring_slots) * kS2Band;
 #pragma unroll
           for (int e = 0; e < 2; ++e)
             if (act[e]) {
               const float tf = (float)(Sbar[e] * (double)Pv[e]);
-              const float old = line[e];
+              const float old = e == 0 ? old_t.x : old_t.y;
               line[e] = tf;
               Y[e] += (double)tf - (double)old;
             }
