@@ -2,6 +2,7 @@
 // sequencing.  No allocation, no synchronisation (except rosa_b200_read_status).
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <limits>
 
 #include "common.cuh"
@@ -17,7 +18,17 @@ using namespace rosa;
 
 namespace {
 
-constexpr size_t kPartialBudgetBytes = (size_t)6 << 30;  // target size of the VJP partial buffers
+// Target size of the VJP partial buffers (per-item partial gradient rows + window ring): items
+// grow (more bands per CTA) until they fit.  ROSA_B200_PARTIAL_BUDGET_MB overrides it for
+// experiments; the sizing function and the call read the same value.
+size_t partial_budget_bytes() {
+  static const size_t bytes = [] {
+    const char* v = std::getenv("ROSA_B200_PARTIAL_BUDGET_MB");
+    const long mb = v != nullptr ? std::atol(v) : 0;
+    return mb > 0 ? (size_t)mb << 20 : (size_t)6 << 30;
+  }();
+  return bytes;
+}
 
 struct FwdLayout {
   PlanLayout plan;
@@ -105,7 +116,7 @@ VjpLayout vjp_layout(int64_t N, int H, int D, int Hv, int Dv, int64_t S, int64_t
     // the window ring (one line of kVjpBand floats per horizon step and item) counts against
     // the same budget: fewer, longer items shrink it together with the partial rows
     const size_t ring = (size_t)items * H * l.ring_slots * kVjpBand * sizeof(float);
-    if ((size_t)rows * H * per_row + ring <= kPartialBudgetBytes ||
+    if ((size_t)rows * H * per_row + ring <= partial_budget_bytes() ||
         (int64_t)g * kVjpBand >= max_len)
       break;
   }
