@@ -132,6 +132,7 @@ class RosaRuntime:
         self._lengths: Optional[Tensor] = None
         self._sequence_ids: Optional[Tuple[int, ...]] = None
         self._ids_fixed = False
+        self._last_update: Optional[torch.cuda.Event] = None   # orders updates across streams
 
     # ------------------------------------------------------------------ configuration
     @property
@@ -248,8 +249,8 @@ class RosaRuntime:
     # -------------------------------------------------------------------------- state
     def _grow(self, needed: int) -> None:
         """Makes room for `needed` tokens per slot (capacity doubles; old contents are kept)."""
-        if needed <= self._capacity:
-            return
+        if needed <= self._capacity and self._capacity > 0:
+            return      # (a first update without tokens still allocates the minimum capacity)
         capacity = max(_MIN_CAPACITY, self._capacity)
         while capacity < needed:
             capacity *= 2
@@ -385,6 +386,10 @@ class RosaRuntime:
         run_on = stream if stream is not None else current
         if stream is not None:
             stream.wait_stream(current)   # the inputs were produced on the caller's stream
+        if self._last_update is not None:
+            # the state is shared by all updates: whatever stream the previous one ran on, this
+            # one starts after it (the C ABI wants calls that share a state ordered)
+            run_on.wait_event(self._last_update)
         with torch.cuda.stream(run_on):
             self._grow(max(after))
             flat_q = query_symbols.reshape(-1, heads).contiguous()
@@ -406,8 +411,11 @@ class RosaRuntime:
                 values = torch.where(end.unsqueeze(-1) >= 0, values,
                                      torch.zeros((), dtype=output_dtype, device=device))
                 result = (values, end)
-            for tensor in (flat_q, flat_k, flat_p, dev_offsets, workspace):
+            for tensor in (flat_q, flat_k, flat_p, dev_offsets, workspace, self._key_masks,
+                           self._query_history, self._payload_history, self._lengths):
                 tensor.record_stream(run_on)
+            self._last_update = torch.cuda.Event()
+            self._last_update.record(run_on)
         if stream is None:
             if async_op:
                 event = torch.cuda.Event()

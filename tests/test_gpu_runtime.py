@@ -260,3 +260,79 @@ def test_c_abi_reports_capacity_and_bad_offsets_without_touching_state():
     words = km.view(S, H, 2, cap // 32).cpu().numpy().astype("uint32")
     assert int(words[0, 0, 1, 1]) == 0xF0000000 and int(words[1, 1, 1, 0]) == 0x1F8
     assert int(words[:, :, 0].sum()) == 0
+
+
+def test_updates_on_different_streams_are_ordered_and_empty_first_update_works():
+    """The state is shared by all updates: an update on an explicit stream followed by one on
+    another stream must see the first one's appended tokens; a first update without tokens is
+    accepted (the reference accepts zero-token updates)."""
+    from rosa_soft_b200 import RosaRuntime
+    H, Hp, bits, W, T = 3, 1, 3, 12, 700
+    q = _symbols((T, H), bits, 91, repeat=0.4)
+    k = _symbols((T, H), bits, 92, repeat=0.4)
+    p = _symbols((T, Hp), 8, 93)
+    want_out, want_end = _oracle_streams(q, k, p, [T], W)
+    rt = RosaRuntime(H, Hp, bits, 8, W)
+    empty = torch.zeros((0, H), dtype=torch.uint8, device=DEV)
+    out0, end0 = rt.update_packed(empty, empty, torch.zeros((0, Hp), dtype=torch.uint8, device=DEV),
+                                  cu_seqlens=torch.tensor([0, 0], dtype=torch.int32, device=DEV))
+    assert out0.shape == (0, H) and end0.shape == (0, H)
+    streams = [torch.cuda.Stream(), torch.cuda.Stream(), None]
+    outs, ends, works = [], [], []
+    cuts = [0, 300, 301, T]
+    dev = lambda a: torch.from_numpy(a).to(DEV)
+    for (a, b), st in zip(zip(cuts[:-1], cuts[1:]), streams):
+        cu = torch.tensor([0, b - a], dtype=torch.int32, device=DEV)
+        works.append(rt.update_packed(dev(q[a:b]), dev(k[a:b]), dev(p[a:b]), cu_seqlens=cu, stream=st,
+                                      async_op=st is not None))
+    for w in works:
+        out, end = w.wait() if hasattr(w, "wait") else w
+        outs.append(out)
+        ends.append(end)
+    torch.cuda.synchronize()
+    assert np.array_equal(torch.cat(outs).cpu().numpy(), want_out)
+    assert np.array_equal(torch.cat(ends).cpu().numpy(), want_end)
+
+
+def test_custom_class_matches_the_python_runtime_and_the_reference_fixture():
+    """torch.classes.rosa_soft.RosaRuntime (constructor and methods of the reference's class,
+    rosa_soft/csrc/rosa_runtime.cpp:570-582) over the same streaming entry point."""
+    import rosa_soft_b200  # noqa: F401  (registers the class)
+    z = np.load(os.path.join(GOLDEN, "runtime_cases.npz"))
+    H, Hp, bits, W = z["c1_q"].shape[1], z["c1_payload"].shape[1], 2, int(z["c1_W"])
+    rt = torch.classes.rosa_soft.RosaRuntime(H, Hp, bits, 8, W)
+    cu = torch.from_numpy(z["c1_cu"])            # int64 on the host, like the reference takes it
+    out, end = rt.update_packed(cu, torch.from_numpy(z["c1_q"]).to(DEV),
+                                torch.from_numpy(z["c1_k"]).to(DEV),
+                                torch.from_numpy(z["c1_payload"]).to(DEV))
+    assert np.array_equal(out.cpu().numpy(), z["c1_out"])
+    assert np.array_equal(end.cpu().numpy(), z["c1_end"])
+    states, edges, payload_symbols, automata, sequences, logical = rt.stats()
+    slots = len(z["c1_cu"]) - 1
+    assert (states, edges, automata, sequences) == (0, 0, slots * H, slots)
+    assert payload_symbols == int(z["c1_cu"][-1]) * Hp and logical > 0
+    with pytest.raises(RuntimeError, match="slot count is fixed"):
+        rt.update_packed(cu[:2].clone(), torch.zeros((int(cu[1]), H), dtype=torch.uint8, device=DEV),
+                         torch.zeros((int(cu[1]), H), dtype=torch.uint8, device=DEV),
+                         torch.zeros((int(cu[1]), Hp), dtype=torch.uint8, device=DEV))
+    rt.reset()
+    # chunked after a reset: two updates give the one-shot result
+    lengths = np.diff(z["c1_cu"])
+    half = lengths // 2
+    starts = z["c1_cu"][:-1]
+    parts_out, parts_end = [], []
+    for lo, hi in ((np.zeros_like(half), half), (half, lengths)):
+        idx = np.concatenate([np.arange(s + a, s + b) for s, a, b in zip(starts, lo, hi)])
+        ccu = torch.from_numpy(np.concatenate([[0], np.cumsum(hi - lo)]).astype(np.int32))
+        o, e = rt.update_packed(ccu, torch.from_numpy(z["c1_q"][idx]).to(DEV),
+                                torch.from_numpy(z["c1_k"][idx]).to(DEV),
+                                torch.from_numpy(z["c1_payload"][idx]).to(DEV))
+        parts_out.append((idx, o.cpu().numpy(), e.cpu().numpy()))
+    got_out = np.empty_like(z["c1_out"])
+    got_end = np.empty_like(z["c1_end"])
+    for idx, o, e in parts_out:
+        got_out[idx], got_end[idx] = o, e
+    assert np.array_equal(got_out, z["c1_out"]) and np.array_equal(got_end, z["c1_end"])
+    rt.close()
+    with pytest.raises(RuntimeError, match="closed"):
+        rt.reset()
