@@ -196,7 +196,7 @@ __device__ __forceinline__ uint32_t s1_group(const ColWindow<NG, kWindowed, kDro
 // vjp_sweep1_kernel<NG, true, ...> (analytic softmax reference only); the dropout keep flags go
 // out as one 64-bit word per thread and block, the layout vjp_sweep2_tiled_kernel reads.
 template <int NG, bool kWindowed, bool kDropout>
-__global__ void __launch_bounds__(kTThreads) vjp_sweep1_tiled_kernel(VjpArgs a) {
+__global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs a) {
   extern __shared__ float4 smem_raw[];
   const S1Smem sm = s1_carve(reinterpret_cast<float*>(smem_raw), NG);
   Item it;
