@@ -496,15 +496,18 @@ class Case:
                                f"heads {hs.start}..{hs.stop - 1}")
             b_off, h_off = shard.dropout_batch_offset, shard.dropout_head_offset(group)
 
-            def step(qq, kk, vv, gg):
+            def step(qq, kk, vv, gg, first_batch=0):
+                # `first_batch`: position of qq[0] inside this rank's share, for callers that
+                # feed the share in slices (the end-to-end pipeline below)
                 for t in (qq, kk, vv):
                     t.grad = None
                     t.requires_grad_(True)
                 torch.cuda.manual_seed(20240229)    # every rank draws the same dropout seed
-                with sharding.dropout_coordinates(b_off, h_off):
+                with sharding.dropout_coordinates(b_off + first_batch, h_off):
                     out = rs.rosa_soft(qq, kk, vv, **kw)
                     out.backward(gg)
                 return [out.detach(), qq.grad, kk.grad, vv.grad]
+            self.batch_elements = nb
         self.step = step
 
     def gather(self, results):
@@ -701,12 +704,80 @@ def main():
     e2e_start = torch.cuda.Event(enable_timing=True)
     e2e_stop = torch.cuda.Event(enable_timing=True)
 
-    def e2e_step():
+    def e2e_serial():
         device_inputs = [h.to(dev, non_blocking=True) for h in host]
         for dst, src in zip(host_out, case.step(*device_inputs)):
             dst.copy_(src, non_blocking=True)
 
+    # Dense workloads: batch elements are independent, so the caller's copies overlap the
+    # operator: the share goes through the public operator in slices of `per` batch elements, the
+    # host-to-device copy of slice c + 1 and the device-to-host copy of slice c - 1 on streams of
+    # their own while slice c computes (dropout coordinates carry the slice's batch position, so
+    # the results are those of the unsliced call).
+    nb = getattr(case, "batch_elements", 0)
+    per = 2 if nb >= 4 else 1
+    slices = [(a, min(nb, a + per)) for a in range(0, nb, per)]
+    pipelined = len(slices) >= 2
+    if pipelined:
+        main = torch.cuda.current_stream(dev)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        staging = [[torch.empty((per,) + tuple(h.shape[1:]), dtype=h.dtype, device=dev)
+                    for h in host] for _ in range(2)]
+        ev_in = [torch.cuda.Event() for _ in slices]
+        ev_free = [None, None]                       # compute that last read a staging set
+
+    def e2e_pipelined():
+        def copy_in(c):
+            a, b = slices[c]
+            with torch.cuda.stream(s_in):
+                if ev_free[c % 2] is not None:
+                    s_in.wait_event(ev_free[c % 2])
+                for dst, h in zip(staging[c % 2], host):
+                    dst[:b - a].copy_(h[a:b], non_blocking=True)
+                ev_in[c].record(s_in)
+
+        s_in.wait_stream(main)
+        copy_in(0)
+        for c, (a, b) in enumerate(slices):
+            if c + 1 < len(slices):
+                copy_in(c + 1)
+            main.wait_event(ev_in[c])
+            results = case.step(*[t[:b - a] for t in staging[c % 2]], first_batch=a)
+            done = torch.cuda.Event()
+            done.record(main)
+            ev_free[c % 2] = done
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for dst, src in zip(host_out, results):
+                    src.record_stream(s_out)
+                    dst[a:b].copy_(src, non_blocking=True)
+        main.wait_stream(s_out)
+        main.wait_stream(s_in)
+
+    e2e_step = e2e_pipelined if pipelined else e2e_serial
+    e2e_how = (f"public operator on {len(slices)} slices of {per} batch element(s) per rank, "
+               f"host copies of neighbouring slices overlapped on two copy streams; output checked "
+               f"bit-equal and gradients to two ulps of their dtype against the unsliced call" if pipelined else
+               "one public-operator call per step, copies and compute on one stream")
     e2e_step()
+    if pipelined:
+        # The sliced pipeline must reproduce the unsliced call: the output bit for bit; the
+        # gradients up to the grouping of their fixed-order partial sums, which follows the
+        # number of work items and so the batch size of a call (a few float32 ulps before the cast).
+        torch.cuda.synchronize(dev)
+        for idx, (got, want) in enumerate(zip(host_out, case.step(*case.inputs))):
+            want = want.cpu()
+            if idx == 0:
+                same = torch.equal(got, want)
+            else:
+                # gradients come back in the input dtype: allow two of its ulps
+                rtol = {torch.bfloat16: 2e-2, torch.float16: 2e-3}.get(got.dtype, 1e-4)
+                same = torch.allclose(got.float(), want.float(), rtol=rtol,
+                                      atol=1e-5 * float(want.float().abs().max()))
+            if not same:
+                err = float((got.float() - want.float()).abs().max())
+                raise SystemExit(f"end-to-end pipeline: result {idx} differs from the unsliced call "
+                                 f"(max abs difference {err:.3e})")
     barrier()
     e2e_start.record()
     for _ in range(args.steps):
@@ -775,7 +846,8 @@ def main():
                    **head_extra},
         "clocks": timing["clocks"],
         "e2e": {"value": head_units * args.steps / (e2e_ms / 1e3) / 1e6, "unit": "M token-heads/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "how": e2e_how},
         "gpu_launches": sum(n for _, n in kernels.values()) * world,
         "peak_device_bytes": timing["peak_bytes"],
         "kernel_ms_per_step": {n: ms / args.steps for n, (ms, _) in sorted(kernels.items())},

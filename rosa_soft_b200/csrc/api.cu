@@ -146,6 +146,25 @@ VjpLayout vjp_layout(int64_t N, int H, int D, int Hv, int Dv, int64_t S, int64_t
   return l;
 }
 
+// A dense batch whose partial rows would not fit the budget at one band per work item is run in
+// slices of whole sequences, one after the other on the caller's stream, each slice with the
+// finest work items and all of them in the same workspace: sequences never interact, so the
+// results are those of one call, the workspace stops growing with the batch, and the finer items
+// balance better than longer items over the whole batch would.  Returns the number of slices;
+// slice i holds S / n + (i < S % n) sequences.
+int64_t vjp_dense_slices(int H, int D, int Dv, int64_t S, int64_t uniform_len, int64_t W, int mask) {
+  if (uniform_len < 2 || S <= 1) return 1;
+  const size_t per_row = sizeof(float4) + sizeof(float) * ((mask & 1 ? D : 0) + (mask & 2 ? D : 0) +
+                                                            (mask & 4 ? Dv : 0));
+  const int64_t items = (uniform_len - 1 + kVjpBand - 1) / kVjpBand;      // per sequence, g = 1
+  const int ring_slots = (W <= uniform_len - 2) ? (int)(W + 1) : 0;
+  const size_t one = (size_t)items * uniform_len * H * per_row +
+                     (size_t)items * H * ring_slots * kVjpBand * sizeof(float);
+  const int64_t fit = std::max<int64_t>(1, (int64_t)(partial_budget_bytes() / one));
+  return fit >= S ? 1 : (S + fit - 1) / fit;
+}
+inline int64_t slice_sequences(int64_t S, int64_t n, int64_t i) { return S / n + (i < S % n ? 1 : 0); }
+
 int check_problem(int64_t N, int H, int D, int Hv, int Dv, const int32_t* cu, int64_t S,
                   int64_t uniform_len, int64_t W, int dtype) {
   ROSA_REQUIRE(dtype >= ROSA_B200_F32 && dtype <= ROSA_B200_BF16,
@@ -394,12 +413,104 @@ ROSA_B200_API int rosa_b200_stream_update(
   return launch_stream_update(a, as_stream(stream));
 }
 
+namespace {
+struct VjpCall {
+  const void *query, *key, *value, *grad_output;
+  int dtype, H, D, Hv, Dv;
+  const int32_t* cu_seqlens;
+  int64_t uniform_len, W;
+  const int32_t *packed_query, *packed_key;
+  const int64_t* dropout_seed;
+  float scale, dropout_p, mismatch_scale;
+  int gradient_mask;
+  bool force_cuda_cores;
+  int64_t batch_offset, head_offset;
+  float *grad_query, *grad_key, *grad_value;
+  void* workspace;
+  size_t workspace_bytes;
+  cudaStream_t stream;
+};
+
+// The backward of `S` whole sequences (`N` tokens) starting at sequence `first_seq` of the call
+// (`first_seq` > 0 only for dense layouts, where it is also the token and dropout batch offset).
+int run_vjp_slice(const VjpCall& c, int64_t first_seq, int64_t N, int64_t S, bool later_slice) {
+  const bool dense = c.cu_seqlens == nullptr;
+  const int H = c.H, D = c.D, Hv = c.Hv, Dv = c.Dv;
+  const VjpLayout l = vjp_layout(N, H, D, Hv, Dv, S, c.uniform_len, dense, c.W, c.gradient_mask);
+  ROSA_REQUIRE(c.workspace_bytes >= l.bytes, "workspace too small: need %zu bytes, got %zu",
+               l.bytes, c.workspace_bytes);
+  ROSA_REQUIRE(l.items_upper * (int64_t)H <= std::numeric_limits<int32_t>::max(),
+               "too many work items: items * heads exceeds the CUDA grid limit");
+  cudaStream_t st = c.stream;
+  char* ws = static_cast<char*>(c.workspace);
+  const size_t esz = c.dtype == ROSA_B200_F32 ? 4 : 2;
+  const int64_t tok = first_seq * c.uniform_len;          // first token of the slice
+  auto at = [](const void* p, size_t bytes) { return static_cast<const char*>(p) + bytes; };
+
+  VjpArgs a{};
+  a.plan = make_plan(c.workspace, l.plan, c.cu_seqlens, N, S, c.uniform_len,
+                     l.bands_per_item * kVjpBand);
+  a.plan.keep_mma_status = later_slice ? 1 : 0;
+  a.q = at(c.query, (size_t)tok * H * D * esz);
+  a.k = at(c.key, (size_t)tok * H * D * esz);
+  a.v = at(c.value, (size_t)tok * Hv * Dv * esz);
+  a.go = at(c.grad_output, (size_t)tok * H * Dv * esz);
+  a.dtype = c.dtype;
+  a.N = N; a.H = H; a.D = D; a.Hv = Hv; a.Dv = Dv;
+  a.W = (int)c.W;
+  a.group = H / Hv;
+  a.bands_per_item = l.bands_per_item;
+  a.qsym = c.packed_query + tok * H;                      // dense symbols: [sequence][head][token]
+  a.ksym = c.packed_key + tok * H;
+  a.sym_seq_stride = dense ? (int64_t)H * c.uniform_len : 0;
+  a.sym_head_stride = dense ? c.uniform_len : N;
+  a.vbits = reinterpret_cast<uint32_t*>(ws + l.vbits_off);
+  a.vwords = l.vwords;
+  a.seed = c.dropout_seed;
+  a.scale = c.scale;
+  a.dropout_p = c.dropout_p;
+  a.inv_keep = 1.0f / (1.0f - c.dropout_p);
+  a.mismatch_scale = c.mismatch_scale;
+  a.mask = c.gradient_mask;
+  a.force_cuda_core_contraction = c.force_cuda_cores;
+  a.batch_offset = (uint32_t)(c.batch_offset + first_seq);
+  a.head_offset = (uint32_t)c.head_offset;
+  a.ckpt = reinterpret_cast<int2*>(ws + l.ckpt_off);
+  a.keepbits = reinterpret_cast<uint32_t*>(ws + l.keep_off);
+  a.stat_part = reinterpret_cast<float4*>(ws + l.stat_off);
+  a.rowstat = reinterpret_cast<float4*>(ws + l.rowstat_off);
+  a.ring = reinterpret_cast<float*>(ws + l.ring_off);
+  a.ring_slots = l.ring_slots;
+  a.dq_part = reinterpret_cast<float*>(ws + l.dq_off);
+  a.dk_part = reinterpret_cast<float*>(ws + l.dk_off);
+  a.dv_part = reinterpret_cast<float*>(ws + l.dv_off);
+  a.dq = c.grad_query ? c.grad_query + tok * H * D : nullptr;
+  a.dk = c.grad_key ? c.grad_key + tok * H * D : nullptr;
+  a.dv = c.grad_value ? c.grad_value + tok * Hv * Dv : nullptr;
+
+  launch_build_plan(a.plan, st);
+  ROSA_CUDA_OK(cudaGetLastError());
+  if (l.ring_bytes) ROSA_CUDA_OK(cudaMemsetAsync(a.ring, 0, l.ring_bytes, st));
+  if (int rc = launch_pack_value_bits(a.v, c.dtype, N, Hv, Dv, a.vbits, a.vwords, st)) return rc;
+  if (int rc = launch_vjp_sweep1(a, (int)l.items_upper, st)) return rc;
+  if (int rc = launch_vjp_rowstats(a, st)) return rc;
+  if (int rc = launch_vjp_sweep2(a, (int)l.items_upper, st)) return rc;
+  return launch_vjp_finalize(a, st);
+}
+}  // namespace
+
 ROSA_B200_API size_t rosa_b200_surrogate_vjp_workspace_bytes(int64_t N, int H, int D, int Hv, int Dv,
                                                int64_t num_seq, int64_t uniform_len,
                                                int64_t max_suffix_length, int gradient_mask) {
   const bool dense = uniform_len > 0;
   const int64_t W = std::min<int64_t>(max_suffix_length, dense ? uniform_len : N);
   gradient_mask &= ~ROSA_B200_MASK_CUDA_CORE_CONTRACTION;
+  if (dense) {
+    // the largest slice (slice 0) sizes the workspace that all slices share
+    const int64_t n = vjp_dense_slices(H, D, Dv, num_seq, uniform_len, W, gradient_mask);
+    const int64_t s0 = slice_sequences(num_seq, n, 0);
+    return vjp_layout(s0 * uniform_len, H, D, Hv, Dv, s0, uniform_len, true, W, gradient_mask).bytes;
+  }
   return vjp_layout(N, H, D, Hv, Dv, num_seq, uniform_len, dense, W, gradient_mask).bytes;
 }
 
@@ -434,55 +545,20 @@ ROSA_B200_API int rosa_b200_surrogate_vjp(const void* query, const void* key, co
   const bool dense = cu_seqlens == nullptr;
   if (!dense) uniform_len = 0;
   const int64_t W = std::min<int64_t>(max_suffix_length, dense ? uniform_len : N);
-  const VjpLayout l = vjp_layout(N, H, D, Hv, Dv, num_seq, uniform_len, dense, W, gradient_mask);
-  ROSA_REQUIRE(workspace_bytes >= l.bytes, "workspace too small: need %zu bytes, got %zu", l.bytes,
-               workspace_bytes);
-  ROSA_REQUIRE(l.items_upper * (int64_t)H <= std::numeric_limits<int32_t>::max(),
-               "too many work items: items * heads exceeds the CUDA grid limit");
-  cudaStream_t st = as_stream(stream);
-  char* ws = static_cast<char*>(workspace);
-
-  VjpArgs a{};
-  a.plan = make_plan(workspace, l.plan, cu_seqlens, N, num_seq, uniform_len,
-                     l.bands_per_item * kVjpBand);
-  a.q = query; a.k = key; a.v = value; a.go = grad_output; a.dtype = dtype;
-  a.N = N; a.H = H; a.D = D; a.Hv = Hv; a.Dv = Dv;
-  a.W = (int)W;
-  a.group = H / Hv;
-  a.bands_per_item = l.bands_per_item;
-  a.qsym = packed_query; a.ksym = packed_key;
-  a.sym_seq_stride = dense ? (int64_t)H * uniform_len : 0;
-  a.sym_head_stride = dense ? uniform_len : N;
-  a.vbits = reinterpret_cast<uint32_t*>(ws + l.vbits_off);
-  a.vwords = l.vwords;
-  a.seed = dropout_seed;
-  a.scale = scale;
-  a.dropout_p = dropout_p;
-  a.inv_keep = 1.0f / (1.0f - dropout_p);
-  a.mismatch_scale = mismatch_scale;
-  a.mask = gradient_mask;
-  a.force_cuda_core_contraction = force_cuda_cores != 0;
-  a.batch_offset = (uint32_t)dropout_batch_offset;
-  a.head_offset = (uint32_t)dropout_head_offset;
-  a.ckpt = reinterpret_cast<int2*>(ws + l.ckpt_off);
-  a.keepbits = reinterpret_cast<uint32_t*>(ws + l.keep_off);
-  a.stat_part = reinterpret_cast<float4*>(ws + l.stat_off);
-  a.rowstat = reinterpret_cast<float4*>(ws + l.rowstat_off);
-  a.ring = reinterpret_cast<float*>(ws + l.ring_off);
-  a.ring_slots = l.ring_slots;
-  a.dq_part = reinterpret_cast<float*>(ws + l.dq_off);
-  a.dk_part = reinterpret_cast<float*>(ws + l.dk_off);
-  a.dv_part = reinterpret_cast<float*>(ws + l.dv_off);
-  a.dq = grad_query; a.dk = grad_key; a.dv = grad_value;
-
-  launch_build_plan(a.plan, st);
-  ROSA_CUDA_OK(cudaGetLastError());
-  if (l.ring_bytes) ROSA_CUDA_OK(cudaMemsetAsync(a.ring, 0, l.ring_bytes, st));
-  if (int rc = launch_pack_value_bits(value, dtype, N, Hv, Dv, a.vbits, a.vwords, st)) return rc;
-  if (int rc = launch_vjp_sweep1(a, (int)l.items_upper, st)) return rc;
-  if (int rc = launch_vjp_rowstats(a, st)) return rc;
-  if (int rc = launch_vjp_sweep2(a, (int)l.items_upper, st)) return rc;
-  return launch_vjp_finalize(a, st);
+  VjpCall c{query, key, value, grad_output, dtype, H, D, Hv, Dv, cu_seqlens, uniform_len, W,
+            packed_query, packed_key, dropout_seed, scale, dropout_p, mismatch_scale,
+            gradient_mask, force_cuda_cores != 0, dropout_batch_offset, dropout_head_offset,
+            grad_query, grad_key, grad_value, workspace, workspace_bytes, as_stream(stream)};
+  if (!dense) return run_vjp_slice(c, 0, N, num_seq, false);
+  // dense: slices of whole sequences (one slice unless the partial rows exceed their budget)
+  const int64_t n = vjp_dense_slices(H, D, Dv, num_seq, uniform_len, W, gradient_mask);
+  int64_t first = 0;
+  for (int64_t i = 0; i < n; ++i) {
+    const int64_t count = slice_sequences(num_seq, n, i);
+    if (int rc = run_vjp_slice(c, first, count * uniform_len, count, i > 0)) return rc;
+    first += count;
+  }
+  return 0;
 }
 
 ROSA_B200_API void rosa_b200_profile_enable(int on) { rosa::profile_enable(on != 0); }

@@ -44,6 +44,7 @@ struct Plan {
   int32_t S;
   int32_t uniform_len;
   int32_t item_diagonals;  // diagonals per work item
+  int32_t keep_mma_status; // non-zero: status[1] of an earlier slice of the same call survives
 };
 
 struct PlanLayout {
@@ -81,6 +82,7 @@ inline Plan make_plan(void* ws, const PlanLayout& l, const int32_t* cu, int64_t 
   p.S = (int32_t)S;
   p.uniform_len = (int32_t)uniform_len;
   p.item_diagonals = item_diagonals;
+  p.keep_mma_status = 0;
   return p;
 }
 

@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(kPlanThreads) build_plan_kernel(Plan plan) {
   const int status = s_status;
   if (tid == 0) {
     plan.status[0] = status;
-    plan.status[1] = 0;
+    if (!plan.keep_mma_status) plan.status[1] = 0;
     plan.status[2] = 0;
     plan.status[3] = 0;
   }

@@ -1461,50 +1461,85 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
 
 // ------------------------------------------------------------------ finalize
 // Sums the per-item partials in item order and applies the softsign Jacobian.
-// which: 0 = query, 1 = key, 2 = value.
+// which: 0 = query, 1 = key, 2 = value.  VEC = 4: a thread owns four consecutive components
+// (128-bit loads of the partial rows); VEC = 1 for rows that are not a multiple of four.
+template <int VEC>
 __global__ void vjp_finalize_kernel(VjpArgs a, int which) {
   const int dim = which == 2 ? a.Dv : a.D;
   const int heads = which == 2 ? a.Hv : a.H;
+  const int dimv = dim / VEC;
   // Threads run head-major over (head, token, component): the partial rows of one head and item
   // are contiguous over (token, component), so the reads of a warp coalesce; only the final
   // element access is strided by the head count.
   const int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (lin >= a.N * heads * dim) return;
-  const int hh = (int)(lin / (a.N * dim));
-  const int64_t rem = lin - (int64_t)hh * a.N * dim;
-  const int64_t token = rem / dim;
-  const int d = (int)(rem - token * dim);
+  if (lin >= a.N * heads * dimv) return;
+  const int hh = (int)(lin / (a.N * dimv));
+  const int64_t rem = lin - (int64_t)hh * a.N * dimv;
+  const int64_t token = rem / dimv;
+  const int d = (int)(rem - token * dimv) * VEC;
   const int64_t idx = (token * heads + hh) * dim + d;
   int start, len;
   const int seq = find_segment(a.plan, token, &start, &len);
-  float sum = 0.0f;
+  float sum[VEC];
+#pragma unroll
+  for (int x = 0; x < VEC; ++x) sum[x] = 0.0f;
+  // adds `count` partial rows `stride` floats apart, in order, a few loads in flight at a time
+  auto add_rows = [&](const float* base, int count, int64_t stride) {
+#pragma unroll 4
+    for (int t = 0; t < count; ++t) {
+      if (VEC == 4) {
+        const float4 p = *reinterpret_cast<const float4*>(base + t * stride);
+        sum[0] += p.x; sum[VEC > 1 ? 1 : 0] += p.y; sum[VEC > 2 ? 2 : 0] += p.z;
+        sum[VEC > 3 ? 3 : 0] += p.w;
+      } else {
+        sum[0] += base[t * stride];
+      }
+    }
+  };
   if (seq >= 0 && len >= 2) {
     const int i = (int)(token - start);
     const int nitems = a.plan.item_prefix[seq + 1] - a.plan.item_prefix[seq];
     const int64_t seq_base = a.plan.row_prefix[seq] * a.H;
     const int64_t id = a.plan.item_diagonals;
+    // item t covers diagonals 1 + t id ..: query row i meets it iff 1 + t id <= i, key / value
+    // row iff t id <= len - 2 - i (value rows are shifted by one)
     if (which == 0) {
-      for (int t = 0; t < nitems && 1 + t * id <= i; ++t)
-        sum += a.dq_part[(seq_base + ((int64_t)hh * nitems + t) * len + i) * a.D + d];
+      const int count = i >= 1 ? (int)min((int64_t)nitems, (i - 1) / id + 1) : 0;
+      add_rows(a.dq_part + (seq_base + (int64_t)hh * nitems * len + i) * a.D + d, count,
+               (int64_t)len * a.D);
     } else if (which == 1) {
-      for (int t = 0; t < nitems && t * id <= (int64_t)len - 2 - i; ++t)
-        sum += a.dk_part[(seq_base + ((int64_t)hh * nitems + t) * len + i) * a.D + d];
+      const int64_t room = (int64_t)len - 2 - i;
+      const int count = room >= 0 ? (int)min((int64_t)nitems, room / id + 1) : 0;
+      add_rows(a.dk_part + (seq_base + (int64_t)hh * nitems * len + i) * a.D + d, count,
+               (int64_t)len * a.D);
     } else if (i >= 1) {
+      const int64_t room = (int64_t)len - 1 - i;
+      const int count = room >= 0 ? (int)min((int64_t)nitems, room / id + 1) : 0;
       for (int g = 0; g < a.group; ++g) {
         const int h = hh * a.group + g;
-        for (int t = 0; t < nitems && t * id <= (int64_t)len - 1 - i; ++t)
-          sum += a.dv_part[(seq_base + ((int64_t)h * nitems + t) * len + i) * a.Dv + d];
+        add_rows(a.dv_part + (seq_base + (int64_t)h * nitems * len + i) * a.Dv + d, count,
+                 (int64_t)len * a.Dv);
       }
     }
   }
   const void* src = which == 0 ? a.q : which == 1 ? a.k : a.v;
-  const float xv = load_as_float(src, idx, a.dtype);
-  const float den = 1.0f + fabsf(xv);
   const float coef = which == 2 ? 1.0f : a.mismatch_scale / (2.0f * (float)a.D);
   float* dst = which == 0 ? a.dq : which == 1 ? a.dk : a.dv;
   // the last position of a sequence is never a key: exact zero, whatever the input holds
   const bool never_key = which == 1 && seq >= 0 && token - start == len - 1;
-  dst[idx] = never_key ? 0.0f : coef * sum / (den * den);
+  float out[VEC];
+#pragma unroll
+  for (int x = 0; x < VEC; ++x) {
+    const float xv = load_as_float(src, idx + x, a.dtype);
+    const float den = 1.0f + fabsf(xv);
+    out[x] = never_key ? 0.0f : coef * sum[x] / (den * den);
+  }
+  if (VEC == 4) {
+    *reinterpret_cast<float4*>(dst + idx) = make_float4(out[0], out[VEC > 1 ? 1 : 0],
+                                                        out[VEC > 2 ? 2 : 0], out[VEC > 3 ? 3 : 0]);
+  } else {
+    dst[idx] = out[0];
+  }
 }
 
 template <int DPAD, int DVPAD>
@@ -1653,9 +1688,18 @@ int launch_vjp_finalize(const VjpArgs& a, cudaStream_t stream) {
   const int threads = 256;
   for (int which = 0; which < 3; ++which) {
     if (!(a.mask >> which & 1)) continue;
-    const int64_t total = a.N * (which == 2 ? (int64_t)a.Hv * a.Dv : (int64_t)a.H * a.D);
+    const int dim = which == 2 ? a.Dv : a.D;
+    float* dst = which == 0 ? a.dq : which == 1 ? a.dk : a.dv;
+    const float* part = which == 0 ? a.dq_part : which == 1 ? a.dk_part : a.dv_part;
+    // whole float4 groups and 16-byte aligned rows on both sides: four components per thread
+    const bool vec = dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(dst) |
+                                       reinterpret_cast<uintptr_t>(part)) & 15) == 0;
+    const int64_t total = a.N * (which == 2 ? (int64_t)a.Hv : (int64_t)a.H) * (vec ? dim / 4 : dim);
     const int64_t blocks = (total + threads - 1) / threads;
-    vjp_finalize_kernel<<<(unsigned)blocks, threads, 0, stream>>>(a, which);
+    if (vec)
+      vjp_finalize_kernel<4><<<(unsigned)blocks, threads, 0, stream>>>(a, which);
+    else
+      vjp_finalize_kernel<1><<<(unsigned)blocks, threads, 0, stream>>>(a, which);
     ROSA_CUDA_OK(cudaGetLastError());
   }
   return 0;
