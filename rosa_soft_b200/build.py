@@ -44,7 +44,8 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
     deps = [os.path.join(CSRC, f) for f in CUDA_SOURCES] + [
         os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "bit_match.cuh"),
-        os.path.join(CSRC, "tcgen05.cuh"), os.path.join(CSRC, "vjp_shared.cuh"), os.path.join(CSRC, "vjp_tiled.cuh"), os.path.join(ROOT, "include", "rosa_soft_b200.h")]
+        os.path.join(CSRC, "tcgen05.cuh"), os.path.join(CSRC, "vjp_shared.cuh"), os.path.join(CSRC, "vjp_tiled.cuh"), os.path.join(CSRC, "vjp_tiled_sweep2_kernel.inl"),
+        os.path.join(ROOT, "include", "rosa_soft_b200.h")]
     if not force and _newer(LIB, deps):
         return LIB
     objdir = os.path.join(PKG, "build")
