@@ -7,7 +7,7 @@
 // workload with the switch compiled to "off").
 template <int NV, int NG, bool kDropout, int kPrec>
 #ifndef ROSA_S2_PAIR
-__global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_kernel(VjpArgs a) {
+__global__ void __launch_bounds__(kS2Threads, 3) vjp_sweep2_tiled_kernel(VjpArgs a) {
 #else /* ROSA_S2_PAIR */
 __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpArgs a) {
 #endif /* ROSA_S2_PAIR */
@@ -118,14 +118,11 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
     const int rb_pair_top = block_rb + (kPair && shift == 0 ? 1 : 0);
 #endif /* ROSA_S2_PAIR */
     const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
-    // Rows of at most 8 components (the common shapes): the partial rows that the accumulators
-    // are added to are requested BEFORE the wait for the tensor core, so the round trip to L2
-    // overlaps the wait instead of following it.
-    const bool small = NG == 2 && D <= 8 && (D & 3) == 0 && (Dv & 3) == 0;
-    float4 prior_k[3][2], prior_v[3][2];
+    // where the accumulators of this thread's columns go: worked out before the wait for the
+    // tensor core
     float* dst_k[3];
     float* dst_v[3];
-    bool use3[3];
+    bool use3[3], first3[3];
 #pragma unroll
     for (int ch = 0; ch < 3; ++ch) {
 #ifndef ROSA_S2_PAIR
@@ -146,16 +143,9 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
       const bool first = (b.w == it.w_begin) &&
                          (kPair ? rb_first <= rb_pair_top && rb_first >= b.rb : rb_first == b.rb);
 #endif /* ROSA_S2_PAIR */
+      first3[ch] = first;
       dst_k[ch] = a.dk_part + (it.rowslot + j) * D;
       dst_v[ch] = a.dv_part + (it.rowslot + j + 1) * Dv;
-#pragma unroll
-      for (int d4 = 0; d4 < 2; ++d4) {
-        prior_k[ch][d4] = prior_v[ch][d4] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (small && use3[ch] && !first) {
-          if ((mask & 2) && 4 * d4 < D) prior_k[ch][d4] = reinterpret_cast<const float4*>(dst_k[ch])[d4];
-          if ((mask & 4) && 4 * d4 < Dv) prior_v[ch][d4] = reinterpret_cast<const float4*>(dst_v[ch])[d4];
-        }
-      }
     }
     if (!mma_timed_out && !__all_sync(0xffffffffu, tc::mbar_wait(mbar, mma_phase, 1u << 24)))
       mma_timed_out = true;
@@ -165,63 +155,13 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
     }
     mma_phase ^= 1u;
     tc::fence_after_thread_sync();
-#ifndef ROSA_S2_PAIR
-    if (small) {
-#else /* ROSA_S2_PAIR */
-    if (!flush) {
-      // first block of a pair: its column sums stay in tensor memory
-    } else if (small) {
-#endif /* ROSA_S2_PAIR */
-#pragma unroll
-      for (int ch = 0; ch < 3; ++ch) {
-        if (ch == 2 && warp < 3) continue;
-        if (mask & 2) {
-          float v[16];
-          tc::tmem_ld16(tmem + lane_base + kColK + ch * NK, v);
-          if (use3[ch]) {
-#pragma unroll
-            for (int d4 = 0; d4 < 2; ++d4)
-              if (4 * d4 < D) {
-                float4 o = prior_k[ch][d4];
-                o.x += v[4 * d4]; o.y += v[4 * d4 + 1]; o.z += v[4 * d4 + 2]; o.w += v[4 * d4 + 3];
-                reinterpret_cast<float4*>(dst_k[ch])[d4] = o;
-              }
-          }
-        }
-        if (mask & 4) {
-          float v[16];
-          tc::tmem_ld16(tmem + lane_base + kColV + ch * NV, v);
-          if (use3[ch]) {
-#pragma unroll
-            for (int d4 = 0; d4 < 2; ++d4)
-              if (4 * d4 < Dv) {
-                float4 o = prior_v[ch][d4];
-                o.x += v[4 * d4]; o.y += v[4 * d4 + 1]; o.z += v[4 * d4 + 2]; o.w += v[4 * d4 + 3];
-                reinterpret_cast<float4*>(dst_v[ch])[d4] = o;
-              }
-          }
-        }
-      }
-    } else
+#ifdef ROSA_S2_PAIR
+    if (flush)       // the first block of a pair leaves its column sums in tensor memory
+#endif
 #pragma unroll
     for (int ch = 0; ch < 3; ++ch) {
       if (ch == 2 && warp < 3) continue;
-#ifndef ROSA_S2_PAIR
-      const int c = chunk_start(ch) + 32 * warp + lane;
-      const int j = b.jwin + c;
-#else /* ROSA_S2_PAIR */
-      const int c = chunk_start(ch, L::kTileCols) + 32 * warp + lane;
-      const int j = jbase + c;
-#endif /* ROSA_S2_PAIR */
-      const bool use = use3[ch];
-#ifndef ROSA_S2_PAIR
-      const int i_top = min(j + b.dmax, it.len - 1);
-      const bool first = (b.w == it.w_begin) && (b.rb == i_top / kS2Rows);
-#else /* ROSA_S2_PAIR */
-      const int rb_first = min(j + b.dmax, it.len - 1) / kS2Rows;
-      const bool first = (b.w == it.w_begin) &&
-                         (kPair ? rb_first <= rb_pair_top && rb_first >= b.rb : rb_first == b.rb);
-#endif /* ROSA_S2_PAIR */
+      const bool use = use3[ch], first = first3[ch];
       if (mask & 2) {
         float v[16];
         tc::tmem_ld16(tmem + lane_base + kColK + ch * NK, v);
@@ -232,9 +172,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
             for (int d4 = 0; d4 < 4; ++d4)
               if (4 * d4 < D) {
                 float4* p4 = reinterpret_cast<float4*>(dst) + d4;
-                float4 o = first ? make_float4(0.f, 0.f, 0.f, 0.f) : *p4;
-                o.x += v[4 * d4]; o.y += v[4 * d4 + 1]; o.z += v[4 * d4 + 2]; o.w += v[4 * d4 + 3];
-                *p4 = o;
+                accumulate_row4(p4, first, v[4 * d4], v[4 * d4 + 1], v[4 * d4 + 2], v[4 * d4 + 3]);
               }
           } else {
 #pragma unroll
@@ -255,9 +193,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
               for (int d4 = 0; d4 < 4; ++d4)
                 if (n0 + 4 * d4 < Dv) {
                   float4* p4 = reinterpret_cast<float4*>(dst) + d4;
-                  float4 o = first ? make_float4(0.f, 0.f, 0.f, 0.f) : *p4;
-                  o.x += v[4 * d4]; o.y += v[4 * d4 + 1]; o.z += v[4 * d4 + 2]; o.w += v[4 * d4 + 3];
-                  *p4 = o;
+                  accumulate_row4(p4, first, v[4 * d4], v[4 * d4 + 1], v[4 * d4 + 2], v[4 * d4 + 3]);
                 }
             } else {
 #pragma unroll
@@ -295,10 +231,15 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
                 *reinterpret_cast<const float4*>(s_dq + ((t - 1) * kS2Rows + lane) * 16 + 4 * d4);
             sum[0] += o.x; sum[1] += o.y; sum[2] += o.z; sum[3] += o.w;
           }
+          if ((D & 3) == 0) {
+            accumulate_row4(reinterpret_cast<float4*>(dst) + d4, b.w == it.w_begin, sum[0], sum[1],
+                            sum[2], sum[3]);
+          } else {
 #pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const int d = 4 * d4 + x;
-            if (d < D) dst[d] = (b.w == it.w_begin) ? sum[x] : dst[d] + sum[x];
+            for (int x = 0; x < 4; ++x) {
+              const int d = 4 * d4 + x;
+              if (d < D) dst[d] = (b.w == it.w_begin) ? sum[x] : dst[d] + sum[x];
+            }
           }
         }
       }
