@@ -82,13 +82,16 @@ SIDE_WORKLOADS = ("c2_f32", "c2_bf16", "c3", "c4", "c5", "stream")
 # DRAM bytes (read + write) of one launch of the backward's second sweep per causal pair, from
 # one ncu capture per kernel variant (profiles/); None where no capture backs a figure.
 SWEEP2_DRAM_BYTES_PER_PAIR = {
-    # vjp_sweep2_tiled_kernel<16,2,true,2> on `profile8k`: 1103.7 MB for 1073.6 M pairs
+    # vjp_sweep2_tiled_kernel<16,2,true,2> on `profile8k`: 1096.3 MB for 1073.6 M pairs
     # (profiles/vjp_sweep2_tiled__profile8k_T8192_H32.md); same kernel and controls
-    "metric": 1.028, "profile8k": 1.028, "profile": 1.028, "small": 1.028, "c2_bf16": 1.028,
-    # vjp_sweep2_tiled_kernel<16,4,false,2> on `c3_profile`: 218.8 MB for 268.4 M pairs (same file)
-    "c3": 0.815, "c3_profile": 0.815,
-    # no capture of the float32 / float16 variants: no figure
-    "c2_f32": None, "c4": None,
+    "metric": 1.021, "profile8k": 1.021, "profile": 1.021, "small": 1.021, "c2_bf16": 1.021,
+    # vjp_sweep2_tiled_kernel<16,4,false,2> on `c3_profile`: 215.4 MB for 268.4 M pairs (same file)
+    "c3": 0.803, "c3_profile": 0.803,
+    # vjp_sweep2_tiled_pair_kernel<32,8,true,1> on `c4_profile`: 437.2 MB for 268.4 M pairs (same
+    # file); `c4` runs the same kernel variant on packed sequences
+    "c4": 1.629, "c4_profile": 1.629,
+    # no capture of the float32 variant: no figure
+    "c2_f32": None,
 }
 
 
