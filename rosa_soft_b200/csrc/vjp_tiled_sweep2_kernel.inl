@@ -554,6 +554,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
       // the mismatch-count sum walked backwards (hs ended phase A on the block's last row); the
       // sliding sum Y of Sbar * P over W + 1 rows lives in a ring indexed by the row, so a warp
       // reads and writes one contiguous line per row.
+      int slot = (g.i0 + kS2Rows - 1) % ring_slots;    // ring line of the row, walked downwards
 #pragma unroll 1
       for (int r = kS2Rows - 1; r >= 0; --r) {
         const int i = g.i0 + r;
@@ -568,7 +569,8 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
         bool act[2];
         // the ring line of this row is requested first: while no window product has been alive
         // for W + 2 rows the ring holds zeros and nothing is read
-        float* line = ring + (int64_t)(i % ring_slots) * kS2Band;
+        float* line = ring + (int64_t)slot * kS2Band;
+        slot = (slot == 0 ? ring_slots : slot) - 1;
         float2 old_t = make_float2(0.0f, 0.0f);
         if (live > 0) old_t = *reinterpret_cast<const float2*>(line);
 #pragma unroll
