@@ -585,7 +585,9 @@ def rooflines(case, timing, peaks, name):
         source = "measured (sustained bf16 cuBLAS, MEASURED_PEAKS.json)"
         if tensor_peak is None:
             tensor_peak, source = 1400.0, "fallback"
-        achieved = flop / (k_ms / k_n / 1e3) / 1e12 if k_n else None
+        # work of one launch over the mean launch time: a step may run the sweep once per slice
+        # of the batch, so both are taken per launch (flop * steps / k_n over k_ms / k_n)
+        achieved = flop * steps / (k_ms / 1e3) / 1e12 if k_n else None
         per_pair = SWEEP2_DRAM_BYTES_PER_PAIR.get(name)
         bwd_ms = sum(kernels.get(n, (0.0, 0))[0] for n in ("pack_value_bits", "vjp_sweep1",
                                                              "vjp_rowstats", "vjp_sweep2",
@@ -593,8 +595,10 @@ def rooflines(case, timing, peaks, name):
         out["roofline"] = {
             "bound": "tensor", "kernel": "vjp_sweep2", "achieved": achieved, "peak": tensor_peak,
             "unit": "TFLOP/s", "frac": (achieved / tensor_peak) if achieved else None,
-            "traffic": per_pair * case.pairs if per_pair else None, "peak_source": source,
+            "traffic": per_pair * case.pairs * steps / k_n if per_pair and k_n else None,
+            "peak_source": source,
             "kernel_ms": (k_ms / k_n) if k_n else None,
+            "launches_per_step": (k_n / steps) if steps else None,
             "whole_backward_tflops": flop / (bwd_ms / 1e3) / 1e12 if bwd_ms else None,
             "note": "algorithmic contraction work (6D+4Dv FLOP per causal pair of this rank) over "
                     "the kernel's mean launch time; the kernel is bound by CUDA-core issue (ALU "
