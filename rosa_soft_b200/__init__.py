@@ -69,7 +69,8 @@ BUILD_CAPABILITIES = BuildCapabilities(
 )
 
 from .inference import rosa_hard_inference  # noqa: E402
-from .inspection import HardRouteInspection, inspect_hard_routes  # noqa: E402
+from .inspection import (HardRouteDiagnostics, HardRouteInspection, SymbolHealth,  # noqa: E402
+                         inspect_hard_routes, summarize_hard_routes, symbol_health)
 from .runtime import RosaRuntime  # noqa: E402
 from .soft import rosa_soft, rosa_soft_varlen  # noqa: E402
 
@@ -79,6 +80,10 @@ __all__ = [
     "HardRouteInspection",
     "RosaRuntime",
     "inspect_hard_routes",
+    "summarize_hard_routes",
+    "symbol_health",
+    "HardRouteDiagnostics",
+    "SymbolHealth",
     "rosa_hard_inference",
     "rosa_soft",
     "rosa_soft_varlen",

@@ -464,6 +464,21 @@ def test_route_inspection_matches_oracle_dense_and_packed():
                                      max_suffix_length=W)
     assert np.array_equal(info.selected_route_indices.t().cpu().numpy(), want_route)
     assert np.array_equal(info.selected_match_lengths.t().cpu().numpy(), want_len)
+    # route statistics of the packed case against their definitions on the oracle's routes
+    # (reference: hard_nonnull_route_fraction / hard_route_lag_mean of
+    # rosa_soft/diagnostics.py:264-274, _symbol_health of diagnostics.py:186-207)
+    qp, kp = q.reshape(B * T, H, D), k.reshape(B * T, H, D)
+    diag = rs.summarize_hard_routes(info, qp.to(DEV), kp.to(DEV))
+    rows = np.concatenate([np.arange(n) for n in lengths])
+    hit = want_route > 0
+    assert abs(diag.hard_nonnull_route_fraction - hit.mean()) < 1e-6
+    assert abs(diag.hard_route_lag_mean - (rows[:, None] - want_route)[hit].mean()) < 1e-4
+    assert abs(diag.selected_match_length_mean - want_len[hit].mean()) < 1e-4
+    assert abs(diag.horizon_hit_fraction - (want_len[hit] >= W).mean()) < 1e-6
+    assert abs(diag.query.positive_fraction - float((qp > 0).float().mean())) < 1e-6
+    assert abs(diag.key.sign_margin_low_quantile - float(torch.quantile(kp.abs().reshape(-1), 0.05))) < 1e-5
+    assert abs(diag.key.softsign_derivative_mean
+               - float((1.0 + kp.abs()).square().reciprocal().mean())) < 1e-6
 
 
 def test_hard_inference_with_a_horizon_beyond_the_narrow_key_range(cabi):

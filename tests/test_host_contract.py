@@ -189,3 +189,28 @@ def test_installer_honours_the_reference_build_switches():
     with pytest.raises(RuntimeError, match="USE_CUDA must be"):
         module.resolve_variant({"USE_CUDA": "maybe"})
     assert module._version() == "0.1.0"
+
+
+def test_symbol_health_and_route_summary_on_cpu():
+    """The statistics helpers of the inspection module are plain tensor reductions: checked on
+    CPU against their definitions (reference rosa_soft/diagnostics.py:186-207, 264-274)."""
+    import rosa_soft_b200 as rs
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(3, 50, 4, 6, generator=g)
+    h = rs.symbol_health(x, 0.1)
+    assert abs(h.positive_fraction - float((x > 0).float().mean())) < 1e-7
+    per_bit = (x > 0).float().mean(dim=(0, 1, 2))
+    assert abs(h.bit_imbalance - float((2 * (per_bit - 0.5).abs()).mean())) < 1e-7
+    assert abs(h.sign_margin_low_quantile - float(torch.quantile(x.abs().reshape(-1), 0.1))) < 1e-6
+    routes = torch.tensor([[[0, 1, 0, 2, 4]]])            # [B=1, H=1, T=5]
+    lens = torch.tensor([[[0, 1, 0, 3, 2]]])
+    info = rs.HardRouteInspection(routes, lens, 3, torch.arange(5))
+    d = rs.summarize_hard_routes(info, x, x)
+    assert abs(d.hard_nonnull_route_fraction - 0.6) < 1e-7
+    assert abs(d.hard_route_lag_mean - ((1 - 1) + (3 - 2) + (4 - 4)) / 3) < 1e-7
+    assert abs(d.selected_match_length_mean - 2.0) < 1e-7
+    assert abs(d.horizon_hit_fraction - 1 / 3) < 1e-7
+    empty = rs.HardRouteInspection(torch.zeros(1, 1, 4, dtype=torch.int64),
+                                   torch.zeros(1, 1, 4, dtype=torch.int64), 3, torch.arange(4))
+    assert rs.summarize_hard_routes(empty, x, x).hard_route_lag_mean != \
+        rs.summarize_hard_routes(empty, x, x).hard_route_lag_mean      # NaN
