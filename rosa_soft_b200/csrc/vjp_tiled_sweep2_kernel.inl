@@ -5,6 +5,18 @@
 // one template with a constant switch because the unpaired kernel's generated code proved
 // sensitive to the mere presence of the pairing logic (62.8 -> 69.3 ms on the long-match
 // workload with the switch compiled to "off").
+#ifdef ROSA_S2_PAIR
+#define S2_TILE_C tCb            /* the cells of the current block inside the 288-column area */
+#define S2_TILE_P tPb
+#define S2_CHUNK(ch) chunk_start(ch, L::kTileCols)
+#define S2_KV_FIRST kv_accumulate /* the second block of a pair adds to the first one's sums */
+#else
+#define S2_TILE_C tC
+#define S2_TILE_P tP
+#define S2_CHUNK(ch) chunk_start(ch)
+#define S2_KV_FIRST false
+#endif
+
 template <int NV, int NG, bool kDropout, int kPrec>
 #ifndef ROSA_S2_PAIR
 __global__ void __launch_bounds__(kS2Threads, 3) vjp_sweep2_tiled_kernel(VjpArgs a) {
@@ -531,19 +543,11 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
         const uint2 hamw = Hbuf[(r0 >> 2) * kS2Threads + tid];
         const int j1 = g.jwin + cb;
         if (interior)
-#ifndef ROSA_S2_PAIR
-          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, false>(tC, tP, CG, s_rstat, keepw, glut, ulut, v0,
-#else /* ROSA_S2_PAIR */
-          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, false>(tCb, tPb, CG, s_rstat, keepw, glut, ulut, v0,
-#endif /* ROSA_S2_PAIR */
+          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, false>(S2_TILE_C, S2_TILE_P, CG, s_rstat, keepw, glut, ulut, v0,
                                                         v1, s_row, hamw, r0, g.i0, j1, it.len,
                                                         g.skew, cb, mul2, keep_shift, sb, xnext);
         else
-#ifndef ROSA_S2_PAIR
-          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, true>(tC, tP, CG, s_rstat, keepw, glut, ulut, v0,
-#else /* ROSA_S2_PAIR */
-          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, true>(tCb, tPb, CG, s_rstat, keepw, glut, ulut, v0,
-#endif /* ROSA_S2_PAIR */
+          s2_adjoint_group<NG, NC, NP, kPrec == 0, kDropout, true>(S2_TILE_C, S2_TILE_P, CG, s_rstat, keepw, glut, ulut, v0,
                                                        v1, s_row, hamw, r0, g.i0, j1, it.len,
                                                        g.skew, cb, mul2, keep_shift, sb, xnext);
       }
@@ -619,21 +623,11 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
         const int c1 = r + kS2Band - 2 - kS2R * tid;           // column of diagonal 1
         const int off_lo = col_off(c1, CG) + row_off(r), off_hi = col_off(c1 + 1, CG) + row_off(r);
         if ((r & 1) == 0) {
-#ifndef ROSA_S2_PAIR
-          store_pair<NC, kPrec == 0>(tC, off_lo, off_hi, true, Cv[1], Cv[0]);
-          store_pair<NP, kPrec == 0>(tP, off_lo, off_hi, true, pd[1], pd[0]);
-#else /* ROSA_S2_PAIR */
-          store_pair<NC, kPrec == 0>(tCb, off_lo, off_hi, true, Cv[1], Cv[0]);
-          store_pair<NP, kPrec == 0>(tPb, off_lo, off_hi, true, pd[1], pd[0]);
-#endif /* ROSA_S2_PAIR */
+          store_pair<NC, kPrec == 0>(S2_TILE_C, off_lo, off_hi, true, Cv[1], Cv[0]);
+          store_pair<NP, kPrec == 0>(S2_TILE_P, off_lo, off_hi, true, pd[1], pd[0]);
         } else {
-#ifndef ROSA_S2_PAIR
-          store_pair<NC, kPrec == 0>(tC, off_lo, off_hi, false, Cv[1], Cv[0]);
-          store_pair<NP, kPrec == 0>(tP, off_lo, off_hi, false, pd[1], pd[0]);
-#else /* ROSA_S2_PAIR */
-          store_pair<NC, kPrec == 0>(tCb, off_lo, off_hi, false, Cv[1], Cv[0]);
-          store_pair<NP, kPrec == 0>(tPb, off_lo, off_hi, false, pd[1], pd[0]);
-#endif /* ROSA_S2_PAIR */
+          store_pair<NC, kPrec == 0>(S2_TILE_C, off_lo, off_hi, false, Cv[1], Cv[0]);
+          store_pair<NP, kPrec == 0>(S2_TILE_P, off_lo, off_hi, false, pd[1], pd[0]);
         }
       }
     }
@@ -663,13 +657,8 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
         const uint64_t c1 = tc::smem_desc(tc::smem_addr(tC + kTermBytes), kRowGroupBytes, CG);
 #pragma unroll
         for (int ch = 0; ch < 3; ++ch) {
-#ifndef ROSA_S2_PAIR
-          const uint64_t shift = (uint64_t)(((chunk_start(ch) >> 3) * CG) >> 4);
-          tc::mma_bf16(tmem + kColK + ch * NK, c0 + shift, dQz, idK, false);
-#else /* ROSA_S2_PAIR */
-          const uint64_t shift = (uint64_t)(((chunk_start(ch, L::kTileCols) >> 3) * CG) >> 4);
-          tc::mma_bf16(tmem + kColK + ch * NK, c0 + shift, dQz, idK, kv_accumulate);
-#endif /* ROSA_S2_PAIR */
+          const uint64_t shift = (uint64_t)(((S2_CHUNK(ch) >> 3) * CG) >> 4);
+          tc::mma_bf16(tmem + kColK + ch * NK, c0 + shift, dQz, idK, S2_KV_FIRST);
           tc::mma_bf16(tmem + kColK + ch * NK, c1 + shift, dQz, idK, true);
         }
       }
@@ -680,13 +669,8 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
         const uint64_t p1 = tc::smem_desc(tc::smem_addr(tP + kTermBytes), kRowGroupBytes, CG);
 #pragma unroll
         for (int ch = 0; ch < 3; ++ch) {
-#ifndef ROSA_S2_PAIR
-          const uint64_t shift = (uint64_t)(((chunk_start(ch) >> 3) * CG) >> 4);
-          tc::mma_bf16(tmem + kColV + ch * NV, p0 + shift, dGhi, idV, false);
-#else /* ROSA_S2_PAIR */
-          const uint64_t shift = (uint64_t)(((chunk_start(ch, L::kTileCols) >> 3) * CG) >> 4);
-          tc::mma_bf16(tmem + kColV + ch * NV, p0 + shift, dGhi, idV, kv_accumulate);
-#endif /* ROSA_S2_PAIR */
+          const uint64_t shift = (uint64_t)(((S2_CHUNK(ch) >> 3) * CG) >> 4);
+          tc::mma_bf16(tmem + kColV + ch * NV, p0 + shift, dGhi, idV, S2_KV_FIRST);
           if (NP == 2) tc::mma_bf16(tmem + kColV + ch * NV, p1 + shift, dGhi, idV, true);
           if (TM::glo) tc::mma_bf16(tmem + kColV + ch * NV, p0 + shift, dGlo, idV, true);
         }
@@ -694,11 +678,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
       if (warp >= 2 && (mask & 1)) {
         // K-major view (row sums): K direction = column groups, M direction = the row groups of
         // the C terms of a column group (M = 64: the rows past the last term alias p*d cores)
-#ifndef ROSA_S2_PAIR
-        const uint64_t kC = tc::smem_desc(tc::smem_addr(tC), CG, kRowGroupBytes);
-#else /* ROSA_S2_PAIR */
-        const uint64_t kC = tc::smem_desc(tc::smem_addr(tCb), CG, kRowGroupBytes);
-#endif /* ROSA_S2_PAIR */
+        const uint64_t kC = tc::smem_desc(tc::smem_addr(S2_TILE_C), CG, kRowGroupBytes);
         const uint64_t dKz0 = tc::smem_desc(tc::smem_addr(bKz), NK / 8 * 128, 128);
         constexpr int kSteps = kS2Win / 16;
         const int part = warp - 2;
@@ -748,3 +728,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
   if (warp == 0) tc::tmem_dealloc(tmem, kTmemCols);
 }
 
+#undef S2_TILE_C
+#undef S2_TILE_P
+#undef S2_CHUNK
+#undef S2_KV_FIRST
