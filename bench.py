@@ -70,6 +70,9 @@ WORKLOADS = {
                        dtype="bfloat16", gen="repeat"),
     "c4_profile": dict(B=1, T=4096, H=32, D=16, Hv=8, Dv=32, W=64, scale=1.0, p=0.05, m=9.0,
                        dtype="float16", gen="randn"),
+    # a shape outside the register-tiled kernels (symbols wider than 16 bits)
+    "d24_profile": dict(B=1, T=4096, H=32, D=24, Hv=8, Dv=32, W=64, scale=1.0, p=0.05, m=9.0,
+                        dtype="float16", gen="randn"),
     "c5_profile": dict(kind="inference", B=8, T=16384, H=64, D=32, Hv=64, Dv=8, W=32, scale=1.0,
                        p=0.0, m=3.0, dtype="float32", gen="symbols"),
     "stream_profile": dict(kind="stream", B=8, T=16384, H=64, D=8, Hv=64, Dv=8, W=32, chunk=2048,

@@ -990,13 +990,8 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
 #pragma unroll
               for (int d4 = 0; d4 < 4; ++d4) {
                 if (n0 + 4 * d4 < dim) {
-                  float4* p4 = reinterpret_cast<float4*>(dst) + d4;
-                  float4 o = first ? make_float4(0.f, 0.f, 0.f, 0.f) : *p4;
-                  o.x += v[4 * d4 + 0];
-                  o.y += v[4 * d4 + 1];
-                  o.z += v[4 * d4 + 2];
-                  o.w += v[4 * d4 + 3];
-                  *p4 = o;
+                  accumulate_row4(reinterpret_cast<float4*>(dst) + d4, first, v[4 * d4 + 0],
+                                  v[4 * d4 + 1], v[4 * d4 + 2], v[4 * d4 + 3]);
                 }
               }
             } else {

@@ -318,23 +318,6 @@ __device__ __forceinline__ void s2_adjoint_group(
   }
 }
 
-// Adds four accumulator values to a partial gradient row that this CTA alone writes: the first
-// touch stores, later ones go out as one vector reduction to L2 instead of a load, four adds and
-// a store, so no thread waits for the old value.  The touches of one address come from different
-// threads of the CTA in different row blocks, always with a CTA barrier in between, which orders
-// them; the sum is therefore still formed in a fixed order.  (The reduction unit flushes
-// subnormal float32 values to zero.)
-__device__ __forceinline__ void accumulate_row4(float4* p, bool first, float a, float b, float c,
-                                                float d) {
-  if (first) {
-    *p = make_float4(a, b, c, d);
-  } else {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
-                 "f"(d)
-                 : "memory");
-  }
-}
-
 struct S2Geom {
   int w, rb, dmin, dmax, rb_lo, i0, first_row, skew, jwin;
   int64_t ck_idx;
