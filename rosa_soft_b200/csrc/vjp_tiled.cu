@@ -27,6 +27,14 @@ constexpr int kTThreads = kTBand / kTR;         // threads per CTA
 constexpr int kTWarps = kTThreads / 32;
 constexpr int kTRows = kVjpRows;                // rows per checkpointed block
 constexpr int kTWin = kTBand + kTRows;          // window columns of a block
+// The column tables of a block (key symbols, symbols leaving the horizon, first hash round of the
+// route, value sign nibbles) cover 272 key positions; the next block of the band needs the same
+// positions moved by 16.  The tables therefore SLIDE inside a longer buffer: a block computes
+// only its 16 entering columns and moves the base up; every 17th block the surviving 256 columns
+// go back to the start (source [272, 528), destination [0, 256) and the entering columns
+// [256, 272) are pairwise disjoint, so the step needs no barrier of its own).
+constexpr int kTSlide = kTBand;
+constexpr int kTTab = kTWin + kTSlide;          // entries per table
 static_assert(kTRows == 16 && kTBand % 128 == 0, "geometry assumed by the register windows");
 
 struct S1Smem {
@@ -43,17 +51,17 @@ struct S1Smem {
 };
 
 __host__ __device__ constexpr int s1_smem_words(int ng) {
-  return 5 * kTWin + 2 * kTRows + 64 + 2 * kTRows * kTWarps + kTRows * ng * 16;
+  return 5 * kTTab + 2 * kTRows + 64 + 2 * kTRows * kTWarps + kTRows * ng * 16;
 }
 
 __device__ __forceinline__ S1Smem s1_carve(float* base, int ng) {
   S1Smem s;
   int* w = reinterpret_cast<int*>(base);
-  s.s_k = w;                                        w += kTWin;
-  s.s_kold = w;                                     w += kTWin;
-  s.s_h1 = reinterpret_cast<uint32_t*>(w);          w += kTWin;
-  s.s_vb0 = reinterpret_cast<uint32_t*>(w);         w += kTWin;
-  s.s_vb1 = reinterpret_cast<uint32_t*>(w);         w += kTWin;
+  s.s_k = w;                                        w += kTTab;
+  s.s_kold = w;                                     w += kTTab;
+  s.s_h1 = reinterpret_cast<uint32_t*>(w);          w += kTTab;
+  s.s_vb0 = reinterpret_cast<uint32_t*>(w);         w += kTTab;
+  s.s_vb1 = reinterpret_cast<uint32_t*>(w);         w += kTTab;
   s.s_q = w;                                        w += kTRows;
   s.s_qold = w;                                     w += kTRows;
   s.glut = reinterpret_cast<float*>(w);             w += 64;
@@ -235,6 +243,7 @@ __global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs 
       hs[e] = 0;
     }
     const int rb_lo = dmin / kTRows, rb_hi = (it.len - 1) / kTRows;
+    int tab_base = 0;                           // window column 0 inside the table buffers
     const int64_t ck_band = it.ck_base + vjp_ck_before(it.len, w);
     for (int rb = rb_lo; rb <= rb_hi; ++rb) {
       const int i0 = rb * kTRows;                 // rows i0 .. i0 + 15, masked where absent
@@ -243,18 +252,43 @@ __global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs 
       const int skew = first_row - i0;
       const int64_t ck_idx = ck_band + (rb - rb_lo);
       __syncthreads();
-      // ---- block tables
-      for (int c = tid; c < kTWin; c += kTThreads) {
+      // ---- block tables: entry `at` of the buffers describes window column c
+      auto fill_col = [&](int at, int c) {
         const int j = jwin0 + c;
         const bool in = j >= 0 && j < it.len - 1;
-        sm.s_k[c] = in ? __ldg(k + j) : 0;
+        sm.s_k[at] = in ? __ldg(k + j) : 0;
         const int jo = j - W - 1;
-        sm.s_kold[c] = (kWindowed && jo >= 0 && jo < it.len) ? __ldg(k + jo) : 0;
-        if (kDropout) sm.s_h1[c] = dropout_route_open((uint32_t)(j + 1));
+        sm.s_kold[at] = (kWindowed && jo >= 0 && jo < it.len) ? __ldg(k + jo) : 0;
+        if (kDropout) sm.s_h1[at] = dropout_route_open((uint32_t)(j + 1));
         const uint32_t bits = in ? __ldg(vb + j + 1) : 0u;
-        sm.s_vb0[c] = spread_nibbles(bits & 0xffffu);
-        if (NG > 4) sm.s_vb1[c] = spread_nibbles(bits >> 16);
+        sm.s_vb0[at] = spread_nibbles(bits & 0xffffu);
+        if (NG > 4) sm.s_vb1[at] = spread_nibbles(bits >> 16);
+      };
+      if (rb == rb_lo) {                          // a band starts: the whole window
+        tab_base = 0;
+        for (int c = tid; c < kTWin; c += kTThreads) fill_col(c, c);
+      } else {                                    // the window moved up by 16 columns
+        if (tab_base < kTSlide) {
+          tab_base += kTRows;
+        } else {
+          for (int e = tid; e < kTWin - kTRows; e += kTThreads) {
+            const int from = kTSlide + kTRows + e;
+            sm.s_k[e] = sm.s_k[from];
+            if (kWindowed) sm.s_kold[e] = sm.s_kold[from];
+            if (kDropout) sm.s_h1[e] = sm.s_h1[from];
+            sm.s_vb0[e] = sm.s_vb0[from];
+            if (NG > 4) sm.s_vb1[e] = sm.s_vb1[from];
+          }
+          tab_base = 0;
+        }
+        if (tid < kTRows) fill_col(tab_base + kTBand + tid, kTBand + tid);
       }
+      S1Smem win = sm;                            // the tables as the block's window sees them
+      win.s_k += tab_base;
+      win.s_kold += tab_base;
+      win.s_h1 += tab_base;
+      win.s_vb0 += tab_base;
+      win.s_vb1 += tab_base;
       if (tid < kTRows) {
         const int i = i0 + tid;
         const bool in = i >= first_row && i <= it.len - 1;
@@ -293,11 +327,11 @@ __global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs 
       // window column of (row 0, diagonal 3 of this thread); a multiple of 4
       const int col0 = kTBand - kTR - kTR * tid;
       ColWindow<NG, kWindowed, kDropout> cw;
-      load_quad<NG, kWindowed, kDropout>(cw, sm, col0, 0);
+      load_quad<NG, kWindowed, kDropout>(cw, win, col0, 0);
       uint32_t keep_lo = 0u, keep_hi = 0u;
 #pragma unroll 1
       for (int r0 = 0; r0 < kTRows; r0 += 4) {
-        load_quad<NG, kWindowed, kDropout>(cw, sm, col0 + r0 + 4 < kTWin ? col0 + r0 + 4 : col0 + r0, 4);
+        load_quad<NG, kWindowed, kDropout>(cw, win, col0 + r0 + 4 < kTWin ? col0 + r0 + 4 : col0 + r0, 4);
         float es[4] = {0.0f, 0.0f, 0.0f, 0.0f}, eds[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         // key column of (row r0, diagonal 0 of this thread)
         const int j_first = jwin0 + col0 + r0 + 3;
