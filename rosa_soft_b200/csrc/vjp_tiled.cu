@@ -252,21 +252,80 @@ __global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs 
       const int skew = first_row - i0;
       const int64_t ck_idx = ck_band + (rb - rb_lo);
       __syncthreads();
-      // ---- block tables: entry `at` of the buffers describes window column c
-      auto fill_col = [&](int at, int c) {
+      // ---- block tables: entry `at` of the buffers describes window column c.  Every global
+      // load of the block (entering columns, row symbols, grad_output of the utility tables) is
+      // issued before the first result is used, so the section costs one round trip to L2, not
+      // three in a row.
+      struct ColRaw { int k, kold; uint32_t bits; };
+      auto load_col = [&](int c) {
         const int j = jwin0 + c;
         const bool in = j >= 0 && j < it.len - 1;
-        sm.s_k[at] = in ? __ldg(k + j) : 0;
         const int jo = j - W - 1;
-        sm.s_kold[at] = (kWindowed && jo >= 0 && jo < it.len) ? __ldg(k + jo) : 0;
-        if (kDropout) sm.s_h1[at] = dropout_route_open((uint32_t)(j + 1));
-        const uint32_t bits = in ? __ldg(vb + j + 1) : 0u;
-        sm.s_vb0[at] = spread_nibbles(bits & 0xffffu);
-        if (NG > 4) sm.s_vb1[at] = spread_nibbles(bits >> 16);
+        ColRaw r;
+        r.k = in ? __ldg(k + j) : 0;
+        r.kold = (kWindowed && jo >= 0 && jo < it.len) ? __ldg(k + jo) : 0;
+        r.bits = in ? __ldg(vb + j + 1) : 0u;
+        return r;
       };
+      auto store_col = [&](int at, int c, const ColRaw& r) {
+        sm.s_k[at] = r.k;
+        sm.s_kold[at] = r.kold;
+        if (kDropout) sm.s_h1[at] = dropout_route_open((uint32_t)(jwin0 + c + 1));
+        sm.s_vb0[at] = spread_nibbles(r.bits & 0xffffu);
+        if (NG > 4) sm.s_vb1[at] = spread_nibbles(r.bits >> 16);
+      };
+      // raw grad_output element (converted after all loads are under way)
+      auto go_raw = [&](int64_t idx) -> uint32_t {
+        return a.dtype == ROSA_B200_F32 ? __ldg(static_cast<const uint32_t*>(a.go) + idx)
+                                        : (uint32_t)__ldg(static_cast<const uint16_t*>(a.go) + idx);
+      };
+      auto go_value = [&](uint32_t bits) {
+        if (a.dtype == ROSA_B200_F32) return __uint_as_float(bits);
+        if (a.dtype == ROSA_B200_F16) return __half2float(__ushort_as_half((unsigned short)bits));
+        return __uint_as_float(bits << 16);
+      };
+      // utility table of (row, value group) e from its four raw elements
+      auto store_ulut = [&](int e, const uint32_t (&raw)[4]) {
+        float gv[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) gv[b] = go_value(raw[b]);
+        float4* dst = reinterpret_cast<float4*>(sm.ulut + e * 16);
+#pragma unroll
+        for (int n4 = 0; n4 < 4; ++n4) {
+          // nibbles 4 n4 .. 4 n4 + 3: bits 2 and 3 fixed by n4, bits 0 and 1 vary
+          const float hi = ((n4 & 1) ? gv[2] : -gv[2]) + ((n4 & 2) ? gv[3] : -gv[3]);
+          dst[n4] = make_float4(hi - gv[0] - gv[1], hi + gv[0] - gv[1], hi - gv[0] + gv[1],
+                                hi + gv[0] + gv[1]);
+        }
+      };
+      auto load_go4 = [&](int e, uint32_t (&raw)[4]) {
+        const int r = e / NG, g = e - r * NG;
+        const int i = i0 + r;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) raw[b] = 0u;     // +0.0 in every dtype
+        if (e < kTRows * NG && i >= first_row && i <= it.len - 1) {
+          const int64_t base = (((int64_t)it.start + i) * a.H + it.h) * a.Dv + 4 * g;
+#pragma unroll
+          for (int b = 0; b < 4; ++b)
+            if (4 * g + b < a.Dv) raw[b] = go_raw(base + b);
+        }
+      };
+      // -- loads
+      ColRaw entering{0, 0, 0u};
+      int q_new = 0, qold_new = 0;
+      if (tid < kTRows) {
+        if (rb != rb_lo) entering = load_col(kTBand + tid);
+        const int i = i0 + tid;
+        const bool in = i >= first_row && i <= it.len - 1;
+        q_new = in ? __ldg(q + i) : 0;
+        qold_new = (kWindowed && in && i - W - 1 >= 0) ? __ldg(q + i - W - 1) : 0;
+      }
+      uint32_t go_first[4];
+      load_go4(tid, go_first);
+      // -- shared-memory side
       if (rb == rb_lo) {                          // a band starts: the whole window
         tab_base = 0;
-        for (int c = tid; c < kTWin; c += kTThreads) fill_col(c, c);
+        for (int c = tid; c < kTWin; c += kTThreads) store_col(c, c, load_col(c));
       } else {                                    // the window moved up by 16 columns
         if (tab_base < kTSlide) {
           tab_base += kTRows;
@@ -281,7 +340,7 @@ __global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs 
           }
           tab_base = 0;
         }
-        if (tid < kTRows) fill_col(tab_base + kTBand + tid, kTBand + tid);
+        if (tid < kTRows) store_col(tab_base + kTBand + tid, kTBand + tid, entering);
       }
       S1Smem win = sm;                            // the tables as the block's window sees them
       win.s_k += tab_base;
@@ -290,30 +349,15 @@ __global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs 
       win.s_vb0 += tab_base;
       win.s_vb1 += tab_base;
       if (tid < kTRows) {
-        const int i = i0 + tid;
-        const bool in = i >= first_row && i <= it.len - 1;
-        sm.s_q[tid] = in ? __ldg(q + i) : 0;
-        sm.s_qold[tid] = (kWindowed && in && i - W - 1 >= 0) ? __ldg(q + i - W - 1) : 0;
+        sm.s_q[tid] = q_new;
+        sm.s_qold[tid] = qold_new;
       }
       // nibble tables: one thread per (row, value group) builds its sixteen signed sums
-      for (int e = tid; e < kTRows * NG; e += kTThreads) {
-        const int r = e / NG, g = e - r * NG;
-        const int i = i0 + r;
-        float gv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (i >= first_row && i <= it.len - 1) {
-          const int64_t base = (((int64_t)it.start + i) * a.H + it.h) * a.Dv + 4 * g;
-#pragma unroll
-          for (int b = 0; b < 4; ++b)
-            if (4 * g + b < a.Dv) gv[b] = load_as_float(a.go, base + b, a.dtype);
-        }
-        float4* dst = reinterpret_cast<float4*>(sm.ulut + e * 16);
-#pragma unroll
-        for (int n4 = 0; n4 < 4; ++n4) {
-          // nibbles 4 n4 .. 4 n4 + 3: bits 2 and 3 fixed by n4, bits 0 and 1 vary
-          const float hi = ((n4 & 1) ? gv[2] : -gv[2]) + ((n4 & 2) ? gv[3] : -gv[3]);
-          dst[n4] = make_float4(hi - gv[0] - gv[1], hi + gv[0] - gv[1], hi - gv[0] + gv[1],
-                                hi + gv[0] + gv[1]);
-        }
+      if (tid < kTRows * NG) store_ulut(tid, go_first);
+      for (int e = tid + kTThreads; e < kTRows * NG; e += kTThreads) {
+        uint32_t raw[4];
+        load_go4(e, raw);
+        store_ulut(e, raw);
       }
       __syncthreads();
       // ---- checkpoint of the thread's four diagonals
