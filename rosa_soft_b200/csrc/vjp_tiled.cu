@@ -251,7 +251,9 @@ __global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs 
       const int first_row = max(i0, dmin);        // rows below it belong to no cell of the band
       const int skew = first_row - i0;
       const int64_t ck_idx = ck_band + (rb - rb_lo);
-      __syncthreads();
+      // No barrier here: every warp has passed the barrier that closes the previous block (all
+      // table reads done), and the threads that still read the per-warp row sums after it are
+      // through before they reach the barrier below, ahead of which nobody writes new sums.
       // ---- block tables: entry `at` of the buffers describes window column c.  Every global
       // load of the block (entering columns, row symbols, grad_output of the utility tables) is
       // issued before the first result is used, so the section costs one round trip to L2, not
