@@ -12,8 +12,9 @@
 // work is enqueued on the current stream under a device guard; nothing synchronises unless
 // ROSA_SOFT_B200_CHECK_STATUS=1 asks for the device status word after every call.
 //
-// Also registered: rosa_soft::hard_inference (batched hard inference), the two *_sharded
-// backward operators that take the dropout coordinate offsets of a shard, and the custom class
+// Also registered: rosa_soft::hard_inference (batched hard inference), the backward operator
+// rosa_soft::surrogate_vjp_sharded (dense or packed) that takes the dropout coordinate offsets
+// of a shard, and the custom class
 // torch.classes.rosa_soft.RosaRuntime (constructor and methods of the reference's class,
 // rosa_soft/csrc/rosa_runtime.cpp:570-582) over the streaming entry point of the C ABI.
 //
