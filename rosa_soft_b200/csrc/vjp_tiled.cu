@@ -323,7 +323,10 @@ __global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs 
         qold_new = (kWindowed && in && i - W - 1 >= 0) ? __ldg(q + i - W - 1) : 0;
       }
       uint32_t go_first[4];
-      load_go4(tid, go_first);
+      // the per-block chores are spread over both warps: warp 0 fetches the entering columns and
+      // the row symbols, warp 1 builds the utility tables and closes the block's row sums
+      const int ue = (tid + kTThreads / 2) & (kTThreads - 1);
+      load_go4(ue, go_first);
       // -- shared-memory side
       if (rb == rb_lo) {                          // a band starts: the whole window
         tab_base = 0;
@@ -355,8 +358,8 @@ __global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs 
         sm.s_qold[tid] = qold_new;
       }
       // nibble tables: one thread per (row, value group) builds its sixteen signed sums
-      if (tid < kTRows * NG) store_ulut(tid, go_first);
-      for (int e = tid + kTThreads; e < kTRows * NG; e += kTThreads) {
+      if (ue < kTRows * NG) store_ulut(ue, go_first);
+      for (int e = ue + kTThreads; e < kTRows * NG; e += kTThreads) {
         uint32_t raw[4];
         load_go4(e, raw);
         store_ulut(e, raw);
@@ -416,13 +419,14 @@ __global__ void __launch_bounds__(kTThreads, 8) vjp_sweep1_tiled_kernel(VjpArgs 
       if (kDropout)
         reinterpret_cast<uint2*>(a.keepbits)[ck_idx * kTThreads + tid] = make_uint2(keep_lo, keep_hi);
       __syncthreads();
-      if (tid < kTRows) {
-        const int i = i0 + tid;
+      const int tr = tid - kTThreads / 2;         // row of the tail, on warp 1
+      if (tr >= 0 && tr < kTRows) {
+        const int i = i0 + tr;
         if (i >= first_row && i <= it.len - 1) {
           float m = ref_top - logf((float)i), z = 0.0f, e = 0.0f;
 #pragma unroll
           for (int ww = 0; ww < kTWarps; ++ww) {
-            const float2 part = sm.wstat[tid * kTWarps + ww];
+            const float2 part = sm.wstat[tr * kTWarps + ww];
             z += part.x;
             e += part.y;
           }
