@@ -13,7 +13,7 @@
 #else
 #define S2_TILE_C tC
 #define S2_TILE_P tP
-#define S2_CHUNK(ch) chunk_start(ch)
+#define S2_CHUNK(ch) ((ch) == 2 ? kS2Band - 32 : chunk_start(ch))
 #define S2_KV_FIRST false
 #endif
 
@@ -138,10 +138,12 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
 #pragma unroll
     for (int ch = 0; ch < 3; ++ch) {
 #ifndef ROSA_S2_PAIR
-      const int c = chunk_start(ch) + 32 * warp + lane;
+      const int c = S2_CHUNK(ch) + 32 * warp + lane;
       const int j = b.jwin + c;
-      // only window columns >= 256 of the last chunk are new: they sit in the last quarter
-      use3[ch] = (ch < 2 || (warp == 3 && c >= 256)) && j >= 0 && j <= it.len - 1 - b.dmin;
+      // the last chunk starts at column 224, past-the-window columns included (its MMA reads
+      // on into the B operand buffers; those lanes are never used): its new columns 256..271
+      // fall into the second lane quarter, whose warp has the shortest MMA issue list
+      use3[ch] = (ch < 2 || (warp == 1 && c >= 256 && c < kS2Win)) && j >= 0 && j <= it.len - 1 - b.dmin;
       const int i_top = min(j + b.dmax, it.len - 1);
       const bool first = (b.w == it.w_begin) && (b.rb == i_top / kS2Rows);
 #else /* ROSA_S2_PAIR */
@@ -172,7 +174,11 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
 #endif
 #pragma unroll
     for (int ch = 0; ch < 3; ++ch) {
+#ifdef ROSA_S2_PAIR
       if (ch == 2 && warp < 3) continue;
+#else
+      if (ch == 2 && warp != 1) continue;
+#endif
       const bool use = use3[ch], first = first3[ch];
       if (mask & 2) {
         float v[16];
