@@ -8,7 +8,7 @@
 #ifdef ROSA_S2_PAIR
 #define S2_TILE_C tCb            /* the cells of the current block inside the 288-column area */
 #define S2_TILE_P tPb
-#define S2_CHUNK(ch) chunk_start(ch, L::kTileCols)
+#define S2_CHUNK(ch) ((ch) == 2 ? kS2Band - 32 : chunk_start(ch, L::kTileCols))
 #define S2_KV_FIRST kv_accumulate /* the second block of a pair adds to the first one's sums */
 #else
 #define S2_TILE_C tC
@@ -147,10 +147,12 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
       const int i_top = min(j + b.dmax, it.len - 1);
       const bool first = (b.w == it.w_begin) && (b.rb == i_top / kS2Rows);
 #else /* ROSA_S2_PAIR */
-      const int c = chunk_start(ch, L::kTileCols) + 32 * warp + lane;
+      const int c = S2_CHUNK(ch) + 32 * warp + lane;
       const int j = jbase + c;
-      // only tile columns >= 256 of the last chunk are new: they sit in the last quarter
-      use3[ch] = flush && (ch < 2 || (warp == 3 && c >= 256)) && j >= 0 && j <= it.len - 1 - b.dmin;
+      // only tile columns >= 256 of the last chunk (which starts at column 224) are new: they sit
+      // in the second lane quarter
+      use3[ch] = flush && (ch < 2 || (warp == 1 && c >= 256 && c < L::kTileCols)) && j >= 0 &&
+                 j <= it.len - 1 - b.dmin;
       // the first block of the item that holds column j: the flush of its pair stores, later
       // ones add
       const int rb_first = min(j + b.dmax, it.len - 1) / kS2Rows;
@@ -174,11 +176,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
 #endif
 #pragma unroll
     for (int ch = 0; ch < 3; ++ch) {
-#ifdef ROSA_S2_PAIR
-      if (ch == 2 && warp < 3) continue;
-#else
       if (ch == 2 && warp != 1) continue;
-#endif
       const bool use = use3[ch], first = first3[ch];
       if (mask & 2) {
         float v[16];
