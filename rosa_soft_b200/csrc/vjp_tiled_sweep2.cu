@@ -9,7 +9,10 @@
 // operand area, and tcgen05.mma contracts that area three ways (column sums C^T qz and
 // (p d)^T gO, row sums C kz) into fp32 accumulators in tensor memory.  The MMAs of block b run
 // while the tables and the forward phase of block b+1 are computed; their accumulators are
-// added to the CTA-owned partial gradient rows just before block b+1 overwrites the operands.
+// added to the CTA-owned partial gradient rows (vector reductions to L2, first touch a store)
+// just before block b+1 overwrites the operands.  The kernel text lives in
+// vjp_tiled_sweep2_kernel.inl and is expanded twice: one block per flush of the column sums for
+// value rows of up to 16 components, two blocks per flush for wider rows.
 //
 // What the two-diagonal tiling buys: key-side tables of four rows are six consecutive columns
 // held in registers (64-bit shared loads), row-only values are loaded once for two cells, on
