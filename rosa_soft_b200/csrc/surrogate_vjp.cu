@@ -997,7 +997,7 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_tc_kernel(VjpArgs a) {
             } else {
 #pragma unroll
               for (int d = 0; d < 16; ++d)
-                if (n0 + d < dim) dst[d] = first ? v[d] : dst[d] + v[d];
+                if (n0 + d < dim) accumulate_row1(dst + d, first, v[d]);
             }
           }
         }

@@ -117,4 +117,13 @@ __device__ __forceinline__ void accumulate_row4(float4* p, bool first, float a, 
   }
 }
 
+// One component of such a row (rows whose width is not a multiple of four).
+__device__ __forceinline__ void accumulate_row1(float* p, bool first, float a) {
+  if (first) {
+    *p = a;
+  } else {
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(a) : "memory");
+  }
+}
+
 }  // namespace rosa

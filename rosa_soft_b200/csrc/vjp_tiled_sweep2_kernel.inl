@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
           } else {
 #pragma unroll
             for (int d = 0; d < 16; ++d)
-              if (d < D) dst[d] = first ? v[d] : dst[d] + v[d];
+              if (d < D) accumulate_row1(dst + d, first, v[d]);
           }
         }
       }
@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
             } else {
 #pragma unroll
               for (int d = 0; d < 16; ++d)
-                if (n0 + d < Dv) dst[d] = first ? v[d] : dst[d] + v[d];
+                if (n0 + d < Dv) accumulate_row1(dst + d, first, v[d]);
             }
           }
         }
@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(kS2Threads) vjp_sweep2_tiled_pair_kernel(VjpAr
 #pragma unroll
             for (int x = 0; x < 4; ++x) {
               const int d = 4 * d4 + x;
-              if (d < D) dst[d] = (b.w == it.w_begin) ? sum[x] : dst[d] + sum[x];
+              if (d < D) accumulate_row1(dst + d, b.w == it.w_begin, sum[x]);
             }
           }
         }
