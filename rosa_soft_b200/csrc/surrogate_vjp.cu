@@ -713,13 +713,13 @@ __global__ void __launch_bounds__(kVjpBand, 2) vjp_sweep2_kernel(VjpArgs a) {
               float* dst = a.dk_part + (it.rowslot + j) * D;
 #pragma unroll
               for (int d = 0; d < DPAD; ++d)
-                if (d < D) dst[d] = first ? acck[d] : dst[d] + acck[d];
+                if (d < D) accumulate_row1(dst + d, first, acck[d]);
             }
             if (do_v) {
               float* dst = a.dv_part + (it.rowslot + j + 1) * a.Dv + dv0;
 #pragma unroll
               for (int d = 0; d < DVPAD; ++d)
-                if (dv0 + d < a.Dv) dst[d] = first ? accv[d] : dst[d] + accv[d];
+                if (dv0 + d < a.Dv) accumulate_row1(dst + d, first, accv[d]);
             }
           }
         }
