@@ -133,7 +133,11 @@ ROSA_B200_API int rosa_b200_hard_forward_static(
  * scalar, required iff dropout_p > 0.  `dropout_batch_offset` / `dropout_head_offset`
  * are added to the sequence ordinal / head index inside the dropout counter so a
  * shard of a larger problem reproduces the masks of the unsharded run.
- * Reduction order is fixed: results are bitwise reproducible run to run. */
+ * Reduction order is fixed: results are bitwise reproducible run to run.
+ * The workspace is sized for exactly the shape AND gradient_mask given to the sizing function
+ * (a dense batch whose partial gradient rows would pass 6 GiB is run in slices of whole
+ * sequences inside that one workspace, and the slice size follows the mask); a call with other
+ * arguments than the ones sized for is refused with "workspace too small" when it needs more. */
 ROSA_B200_API size_t rosa_b200_surrogate_vjp_workspace_bytes(int64_t N, int H, int D, int Hv, int Dv,
                                                int64_t num_seq, int64_t uniform_len,
                                                int64_t max_suffix_length, int gradient_mask);
